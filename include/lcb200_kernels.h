@@ -1,0 +1,108 @@
+/* lcb200_kernels.h -- thin C-ABI layer over the hand-written sm_100a data-movement kernels.
+ *
+ * This is the boundary a binding (cgo / JNI / ctypes / the C++ host layer of this library) talks to:
+ * `extern "C"`, plain pointers and sizes, a CUDA stream passed as an opaque pointer.  Every launcher
+ * enqueues on `stream` (NULL = the legacy default stream) of the device that is current in the
+ * calling thread and returns without waiting.  Return value: 0 on success, otherwise a positive
+ * `cudaError_t` value (1 = invalid value for rejected arguments).
+ *
+ * "ref" lines name the reference code (project-relative path:line) each entry point replaces.
+ */
+#ifndef LCB200_KERNELS_H
+#define LCB200_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *lcbStream; /* cudaStream_t / CUstream */
+
+/* Copy-path selector for lcb_copy_d2d_ex (lcb_copy_d2d always uses LCB_COPY_AUTO). */
+enum lcbCopyPath {
+    LCB_COPY_AUTO = 0,  /* pick by size and alignment                                             */
+    LCB_COPY_VEC = 1,   /* 16/32-byte vector loads+stores; src realigned by warp shuffle if needed */
+    LCB_COPY_TMA = 2,   /* cp.async.bulk global->smem->global ring; needs (src-dst) % 16 == 0       */
+    LCB_COPY_SMALL = 3  /* single small CTA wave, latency path                                     */
+};
+
+/* Device-to-device copy of `bytes` bytes, any alignment, any size (64-bit offsets).  Buffers must not
+ * overlap.  One launch does head, body and tail.
+ * ref: memcpyD2D, driverapi/src/memcopy.cpp:77-158 (dispatcher) and memcpyKernelHighBW /
+ * memcpyKernelLowLatency / memcpyKernelTrailing, driverapi/kernels/memcpy/memcpy.cu:5-27. */
+int lcb_copy_d2d(void *dst, const void *src, size_t bytes, lcbStream stream);
+
+/* Same copy with an explicit path and grid (ctas = 0 selects the default persistent grid).  An
+ * infeasible request (LCB_COPY_TMA with mutually misaligned pointers) returns 1. */
+int lcb_copy_d2d_ex(void *dst, const void *src, size_t bytes, int path, int ctas, lcbStream stream);
+
+/* Fill `count` elements of 1, 2 or 4 bytes with `value` (low bytes used).  dst must be aligned to the
+ * element size.  ref: none -- the reference has no memset (driverapi/include/librecuda.h:37-114);
+ * semantics are those of cuMemsetD8/D16/D32Async. */
+int lcb_memset_d8(void *dst, unsigned char value, size_t count, lcbStream stream);
+int lcb_memset_d16(void *dst, unsigned short value, size_t count, lcbStream stream);
+int lcb_memset_d32(void *dst, unsigned int value, size_t count, lcbStream stream);
+/* path: 0 auto, 1 vector stores, 2 bulk (TMA) stores replayed from one shared-memory tile. */
+int lcb_memset_ex(void *dst, unsigned int value, int elem_bytes, size_t count, int path, int ctas, lcbStream stream);
+
+/* dst[i] = (float)i for i in [0, count), round-to-nearest-even.
+ * ref: grid-indexed fill fixture tests/indexing/write_float.cu:1-4 (+ host check
+ * tests/indexing/main.cpp:82-114), generalised from the constant 1.0f to the element index. */
+int lcb_index_fill_f32(float *dst, size_t count, lcbStream stream);
+
+/* y[i] = a * x[i] + b (single rounding of a*x followed by the add is NOT fused: computed as
+ * __fadd_rn(__fmul_rn(a, x), b) so a host loop compiled without FMA contraction matches bit for bit).
+ * ref: the kernel stage between HtoD and DtoH in the reference's stream tests
+ * (tests/async_kernels/write_float.cu:1-9 is the reference's stand-in compute kernel). */
+int lcb_axpb_f32(float *y, const float *x, float a, float b, size_t count, lcbStream stream);
+
+/* One rank's half of an all-to-all over peer-mapped buffers, fused into one kernel: for every j in
+ * [0, n_ranks) chunk j of `send` (chunk_bytes each) is stored to peer_recv[j] + rank * chunk_bytes.
+ * All pointers 16-byte aligned, chunk_bytes a multiple of 16.  peer_recv is a HOST array of n_ranks
+ * device pointers (n_ranks <= 16).  ref: none (the reference is single-GPU, librecuda.cpp:61). */
+int lcb_alltoall_push(void *const *peer_recv, const void *send, size_t chunk_bytes, int n_ranks, int rank,
+                      lcbStream stream);
+
+/* ---- verification helpers that run on the device (used by tests and the benchmark) ------------- */
+
+/* dst[0..bytes) <- the seeded byte stream: 64-bit word i = mix64(seed + (i+1) * 0x9E3779B97F4A7C15),
+ * little-endian, mix64 = the splitmix64 finaliser.  dst 8-byte aligned. */
+int lcb_fill_splitmix64(void *dst, size_t bytes, uint64_t seed, lcbStream stream);
+
+/* result[0] <- number of positions where a[i] != b[i]; result[1] <- smallest such i (UINT64_MAX if
+ * none).  `result` is device memory for two uint64_t and is overwritten. */
+int lcb_compare_bytes(const void *a, const void *b, size_t bytes, uint64_t *result, lcbStream stream);
+
+/* out[0] <- order-independent 64-bit checksum of the buffer: sum over 8-byte words w_i of
+ * mix64(w_i + i * 0x9E3779B97F4A7C15) modulo 2^64 (a trailing partial word is zero-extended).
+ * `scratch` is device memory for at least lcb_checksum_scratch_bytes() bytes; `out` one uint64_t.
+ * src 8-byte aligned. */
+int lcb_checksum64(const void *src, size_t bytes, uint64_t *scratch, uint64_t *out, lcbStream stream);
+size_t lcb_checksum_scratch_bytes(void);
+
+/* Reads and clears the per-device sticky word that kernels set when a bounded wait (mbarrier) gave
+ * up: 0 = no error.  Synchronises the device. */
+int lcb_device_error_word(unsigned int *out);
+
+/* Library / build identification: "lcb200 <version> sm_100a". */
+const char *lcb_version(void);
+
+/* Override one launch tunable by name (thread counts, unroll, bulk-ring depth ...; the names are the
+ * fields of the Tuning record in the kernel sources).  For sweeps; returns 1 for an unknown name. */
+int lcb_tune(const char *name, int value);
+
+/* CUDA-event stopwatch on a raw stream: start/stop record events on `stream`, elapsed waits for the
+ * stop event and returns milliseconds. */
+int lcb_timer_create(void **timer_out);
+int lcb_timer_start(void *timer, lcbStream stream);
+int lcb_timer_stop(void *timer, lcbStream stream);
+int lcb_timer_elapsed_ms(void *timer, float *ms_out);
+int lcb_timer_destroy(void *timer);
+int lcb_stream_synchronize(lcbStream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LCB200_KERNELS_H */

@@ -1,0 +1,349 @@
+// Multi-GPU entry points: peer access, the shard partitioner, partitioned / all-to-all / broadcast data
+// movement over NVLink, and inter-process buffer sharing.  The reference is single-GPU (one process-global
+// context, driverapi/src/librecuda.cpp:61), so everything here is additive.
+//
+// Own-kernel paths store straight into peer memory with the library's copy kernels (plain vector stores or
+// non-multicast bulk copies); NCCL is used only for the broadcast and all-to-all collectives and is loaded
+// lazily with dlopen so that programs that never call them do not need it.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstring>
+
+#include "internal.h"
+
+using namespace lcu;
+
+libreCudaStatus_t libreCuDeviceCanAccessPeer(int *pCanAccess, LibreCUdevice device, LibreCUdevice peerDevice) {
+    LIBRECUDA_VALIDATE(pCanAccess != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(device != nullptr && peerDevice != nullptr, LIBRECUDA_ERROR_INVALID_DEVICE);
+    if (device == peerDevice) {
+        *pCanAccess = 1;
+        LIBRECUDA_SUCCEED();
+    }
+    LCU_CUDA(cudaDeviceCanAccessPeer(pCanAccess, device->ordinal, peerDevice->ordinal));
+    LIBRECUDA_SUCCEED();
+}
+
+libreCudaStatus_t libreCuCtxEnablePeerAccess(LibreCUcontext peerCtx, unsigned int flags) {
+    LIBRECUDA_VALIDATE(peerCtx != nullptr, LIBRECUDA_ERROR_INVALID_CONTEXT);
+    LIBRECUDA_VALIDATE(flags == 0, LIBRECUDA_ERROR_INVALID_VALUE);
+    LCU_ENSURE_CTX();
+    LibreCUcontext cur = globals().current;
+    const int peer = peerCtx->device->ordinal;
+    if (cur->peers.count(peer)) LIBRECUDA_SUCCEED();
+    LIBRECUDA_ERR_PROPAGATE(bind(cur));
+    cudaError_t err = cudaDeviceEnablePeerAccess(peer, 0);
+    if (err == cudaErrorPeerAccessAlreadyEnabled) {
+        (void)cudaGetLastError();
+        err = cudaSuccess;
+    }
+    LCU_CUDA(err);
+    cur->peers.insert(peer);
+    LIBRECUDA_SUCCEED();
+}
+
+// ---- partitioner ------------------------------------------------------------------------------------------
+
+libreCudaStatus_t libreCuPartitionPlan(size_t totalBytes, int parts, size_t alignBytes, size_t *offsetsOut) {
+    LIBRECUDA_VALIDATE(offsetsOut != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(parts >= 1, LIBRECUDA_ERROR_INVALID_VALUE);
+    if (alignBytes == 0) alignBytes = (size_t)2 << 20;
+    LIBRECUDA_VALIDATE((alignBytes & (alignBytes - 1)) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
+    // equal shares rounded up to the alignment; trailing shards may be short or empty
+    const size_t share = (totalBytes + (size_t)parts - 1) / (size_t)parts;
+    const size_t per = (share + alignBytes - 1) / alignBytes * alignBytes;
+    for (int g = 0; g <= parts; ++g) {
+        const size_t o = per * (size_t)g;
+        offsetsOut[g] = (g == parts || o > totalBytes) ? totalBytes : o;
+    }
+    LIBRECUDA_SUCCEED();
+}
+
+libreCudaStatus_t libreCuMemcpyPartitioned(void *const *dsts, const void *src, size_t totalBytes, int parts,
+                                           size_t alignBytes, const LibreCUstream *streams) {
+    LIBRECUDA_VALIDATE(dsts != nullptr && src != nullptr && streams != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(parts >= 1 && parts <= 64, LIBRECUDA_ERROR_INVALID_VALUE);
+    size_t off[65];
+    LIBRECUDA_ERR_PROPAGATE(libreCuPartitionPlan(totalBytes, parts, alignBytes, off));
+    for (int g = 0; g < parts; ++g) {
+        LIBRECUDA_VALIDATE(dsts[g] != nullptr && streams[g] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    }
+    for (int g = 0; g < parts; ++g) {
+        if (off[g + 1] == off[g]) continue;
+        LIBRECUDA_ERR_PROPAGATE(libreCuMemcpyPeer(dsts[g], static_cast<const uint8_t *>(src) + off[g], off[g + 1] - off[g],
+                                                  streams[g], false));
+    }
+    LIBRECUDA_SUCCEED();
+}
+
+// ---- all-to-all ---------------------------------------------------------------------------------------------
+
+libreCudaStatus_t libreCuAllToAllPush(void *const *peerRecvBufs, const void *sendBuf, size_t chunkBytes, int nRanks,
+                                      int rank, LibreCUstream stream) {
+    LIBRECUDA_VALIDATE(peerRecvBufs != nullptr && sendBuf != nullptr && stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(nRanks >= 1 && nRanks <= 16 && rank >= 0 && rank < nRanks, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE((chunkBytes & 15) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE((reinterpret_cast<uintptr_t>(sendBuf) & 15) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
+    for (int j = 0; j < nRanks; ++j) {
+        LIBRECUDA_VALIDATE(peerRecvBufs[j] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE((reinterpret_cast<uintptr_t>(peerRecvBufs[j]) & 15) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
+    }
+    if (chunkBytes == 0) LIBRECUDA_SUCCEED();
+    Command c;
+    c.kind = Command::AllToAllPush;
+    c.src = sendBuf;
+    c.bytes = chunkBytes;
+    c.rank = rank;
+    c.peers.assign(peerRecvBufs, peerRecvBufs + nRanks);
+    return record(stream, std::move(c));
+}
+
+// ---- NCCL, loaded on first use ------------------------------------------------------------------------------
+namespace {
+
+struct Nccl {
+    void *lib = nullptr;
+    ncclResult_t (*CommInitAll)(ncclComm_t *, int, const int *) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
+    ncclResult_t (*Send)(const void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Recv)(void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Broadcast)(const void *, void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+    std::vector<int> devs;           // devices of the cached communicator group
+    std::vector<ncclComm_t> comms;
+};
+
+Nccl *nccl() {
+    static Nccl n;
+    static int state = 0;
+    if (state == 0) {
+        state = -1;
+        n.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
+        if (n.lib == nullptr) {
+            LIBRECUDA_DEBUG("NCCL unavailable: " << dlerror());
+            return nullptr;
+        }
+        bool ok = true;
+        auto sym = [&](const char *name, void **out) {
+            *out = dlsym(n.lib, name);
+            if (*out == nullptr) ok = false;
+        };
+        sym("ncclCommInitAll", reinterpret_cast<void **>(&n.CommInitAll));
+        sym("ncclCommDestroy", reinterpret_cast<void **>(&n.CommDestroy));
+        sym("ncclGroupStart", reinterpret_cast<void **>(&n.GroupStart));
+        sym("ncclGroupEnd", reinterpret_cast<void **>(&n.GroupEnd));
+        sym("ncclSend", reinterpret_cast<void **>(&n.Send));
+        sym("ncclRecv", reinterpret_cast<void **>(&n.Recv));
+        sym("ncclBroadcast", reinterpret_cast<void **>(&n.Broadcast));
+        sym("ncclGetErrorString", reinterpret_cast<void **>(&n.GetErrorString));
+        if (ok) state = 1;
+    }
+    return state == 1 ? &n : nullptr;
+}
+
+#define LCU_NCCL(n, expr)                                                                                    \
+    do {                                                                                                     \
+        ncclResult_t lcu_nr_ = (expr);                                                                       \
+        if (lcu_nr_ != ncclSuccess) {                                                                        \
+            LIBRECUDA_DEBUG(__FILE__ ":" LIBRECUDA_STR_(__LINE__) ": " #expr " -> " << (n)->GetErrorString(lcu_nr_)); \
+            return LIBRECUDA_ERROR_UNKNOWN;                                                                  \
+        }                                                                                                    \
+    } while (0)
+
+libreCudaStatus_t nccl_group_for(Nccl *n, const std::vector<int> &devs) {
+    if (n->devs == devs) LIBRECUDA_SUCCEED();
+    for (ncclComm_t c : n->comms) n->CommDestroy(c);
+    n->comms.assign(devs.size(), nullptr);
+    n->devs.clear();
+    LCU_NCCL(n, n->CommInitAll(n->comms.data(), (int)devs.size(), devs.data()));
+    n->devs = devs;
+    LIBRECUDA_SUCCEED();
+}
+
+libreCudaStatus_t check_group(int nDev, const LibreCUstream *streams, std::vector<int> *devs) {
+    LIBRECUDA_VALIDATE(streams != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(nDev >= 1 && nDev <= 16, LIBRECUDA_ERROR_INVALID_VALUE);
+    for (int r = 0; r < nDev; ++r) {
+        LIBRECUDA_VALIDATE(streams[r] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        const int d = streams[r]->ctx->device->ordinal;
+        for (int q : *devs) LIBRECUDA_VALIDATE(q != d, LIBRECUDA_ERROR_INVALID_VALUE);  // one stream per device
+        devs->push_back(d);
+    }
+    LIBRECUDA_SUCCEED();
+}
+
+// Every stream waits for the collective's work on all the others, so an operation recorded later on any of
+// them sees the complete result.
+libreCudaStatus_t cross_join(int nDev, const LibreCUstream *streams) {
+    std::vector<cudaEvent_t> done(nDev);
+    for (int r = 0; r < nDev; ++r) {
+        LIBRECUDA_ERR_PROPAGATE(bind(streams[r]->ctx));
+        LCU_CUDA(cudaEventCreateWithFlags(&done[r], cudaEventDisableTiming));
+        LCU_CUDA(cudaEventRecord(done[r], streams[r]->main));
+    }
+    for (int r = 0; r < nDev; ++r) {
+        LIBRECUDA_ERR_PROPAGATE(bind(streams[r]->ctx));
+        for (int q = 0; q < nDev; ++q)
+            if (q != r) LCU_CUDA(cudaStreamWaitEvent(streams[r]->main, done[q], 0));
+    }
+    for (int r = 0; r < nDev; ++r) (void)cudaEventDestroy(done[r]);  // released once the waits have consumed it
+    LIBRECUDA_SUCCEED();
+}
+
+libreCudaStatus_t rebind_current() {
+    LibreCUcontext cur = globals().current;
+    if (cur != nullptr) return bind(cur);
+    LIBRECUDA_SUCCEED();
+}
+
+}  // namespace
+
+// Collectives over several streams of this process submit what those streams have recorded so far and are
+// then enqueued at once (eager submission is within the Commence contract); they are complete after
+// libreCuStreamAwait on the participating streams.
+libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, size_t chunkBytes, int nDev,
+                                  const LibreCUstream *streams, int useNccl) {
+    LIBRECUDA_VALIDATE(recvBufs != nullptr && sendBufs != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    std::vector<int> devs;
+    LIBRECUDA_ERR_PROPAGATE(check_group(nDev, streams, &devs));
+    for (int r = 0; r < nDev; ++r) LIBRECUDA_VALIDATE(recvBufs[r] != nullptr && sendBufs[r] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(commence(streams[r]));
+    if (chunkBytes == 0) LIBRECUDA_SUCCEED();
+    if (useNccl) {
+        Nccl *n = nccl();
+        LIBRECUDA_VALIDATE(n != nullptr, LIBRECUDA_ERROR_NOT_FOUND);
+        LIBRECUDA_ERR_PROPAGATE(nccl_group_for(n, devs));
+        LCU_NCCL(n, n->GroupStart());
+        for (int r = 0; r < nDev; ++r) {
+            const uint8_t *s = static_cast<const uint8_t *>(sendBufs[r]);
+            uint8_t *d = static_cast<uint8_t *>(recvBufs[r]);
+            for (int j = 0; j < nDev; ++j) {
+                LCU_NCCL(n, n->Send(s + (size_t)j * chunkBytes, chunkBytes, ncclUint8, j, n->comms[r], streams[r]->main));
+                LCU_NCCL(n, n->Recv(d + (size_t)j * chunkBytes, chunkBytes, ncclUint8, j, n->comms[r], streams[r]->main));
+            }
+        }
+        LCU_NCCL(n, n->GroupEnd());
+    } else {
+        LIBRECUDA_VALIDATE((chunkBytes & 15) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
+        // rank r must not overwrite a receive slot its peer is still sending from / reading: start after
+        // everything submitted so far on every stream
+        LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+        for (int r = 0; r < nDev; ++r) {
+            LIBRECUDA_ERR_PROPAGATE(bind(streams[r]->ctx));
+            LCU_LCB(lcb_alltoall_push(recvBufs, sendBufs[r], chunkBytes, nDev, r, streams[r]->main));
+        }
+        LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+    }
+    return rebind_current();
+}
+
+libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount, int nDev, const LibreCUstream *streams,
+                                   int useNccl) {
+    LIBRECUDA_VALIDATE(bufs != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    std::vector<int> devs;
+    LIBRECUDA_ERR_PROPAGATE(check_group(nDev, streams, &devs));
+    LIBRECUDA_VALIDATE(root >= 0 && root < nDev, LIBRECUDA_ERROR_INVALID_VALUE);
+    for (int r = 0; r < nDev; ++r) LIBRECUDA_VALIDATE(bufs[r] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(commence(streams[r]));
+    if (byteCount == 0 || nDev == 1) LIBRECUDA_SUCCEED();
+    if (useNccl) {
+        Nccl *n = nccl();
+        LIBRECUDA_VALIDATE(n != nullptr, LIBRECUDA_ERROR_NOT_FOUND);
+        LIBRECUDA_ERR_PROPAGATE(nccl_group_for(n, devs));
+        LCU_NCCL(n, n->GroupStart());
+        for (int r = 0; r < nDev; ++r)
+            LCU_NCCL(n, n->Broadcast(bufs[root], bufs[r], byteCount, ncclUint8, root, n->comms[r], streams[r]->main));
+        LCU_NCCL(n, n->GroupEnd());
+        return rebind_current();
+    }
+    // Own path, two phases over peer stores.  Phase 1: the root scatters shard g to device g (each byte
+    // leaves the root once).  Phase 2: every non-root device forwards its shard to the other non-root
+    // devices, so the remaining traffic is spread over all NVLink ports instead of the root's alone.
+    size_t off[17];
+    LIBRECUDA_ERR_PROPAGATE(libreCuPartitionPlan(byteCount, nDev, 0, off));
+    LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+    LIBRECUDA_ERR_PROPAGATE(bind(streams[root]->ctx));
+    const uint8_t *src = static_cast<const uint8_t *>(bufs[root]);
+    std::vector<cudaEvent_t> landed(nDev, nullptr);
+    for (int g = 0; g < nDev; ++g) {
+        if (g == root || off[g + 1] == off[g]) continue;
+        LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[g]) + off[g], src + off[g], off[g + 1] - off[g], streams[root]->main));
+        LCU_CUDA(cudaEventCreateWithFlags(&landed[g], cudaEventDisableTiming));
+        LCU_CUDA(cudaEventRecord(landed[g], streams[root]->main));
+    }
+    // the root's own shard goes to everyone from the root
+    if (off[root + 1] > off[root]) {
+        for (int g = 0; g < nDev; ++g) {
+            if (g == root) continue;
+            LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[g]) + off[root], src + off[root], off[root + 1] - off[root],
+                                 streams[root]->main));
+        }
+    }
+    for (int g = 0; g < nDev; ++g) {
+        if (g == root || landed[g] == nullptr) continue;
+        LIBRECUDA_ERR_PROPAGATE(bind(streams[g]->ctx));
+        LCU_CUDA(cudaStreamWaitEvent(streams[g]->main, landed[g], 0));
+        const uint8_t *mine = static_cast<const uint8_t *>(bufs[g]) + off[g];
+        for (int q = 0; q < nDev; ++q) {
+            if (q == root || q == g) continue;
+            LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[q]) + off[g], mine, off[g + 1] - off[g], streams[g]->main));
+        }
+    }
+    for (cudaEvent_t e : landed)
+        if (e) (void)cudaEventDestroy(e);
+    LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+    return rebind_current();
+}
+
+// ---- inter-process sharing -------------------------------------------------------------------------------------
+// handle layout: cudaIpcMemHandle_t (64 bytes) followed by the 8-byte offset of the pointer inside the
+// underlying CUDA allocation.
+
+libreCudaStatus_t libreCuIpcGetMemHandle(void *handle, void *devicePointer) {
+    LIBRECUDA_VALIDATE(handle != nullptr && devicePointer != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LCU_ENSURE_CTX();
+    auto &allocs = globals().allocations;
+    auto it = allocs.find(reinterpret_cast<uintptr_t>(devicePointer));
+    LIBRECUDA_VALIDATE(it != allocs.end(), LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(!it->second.mapped && !it->second.ipc, LIBRECUDA_ERROR_INVALID_VALUE);
+    LCU_CUDA(cudaSetDevice(it->second.device));
+    cudaIpcMemHandle_t h;
+    LCU_CUDA(cudaIpcGetMemHandle(&h, it->second.raw));
+    const uint64_t offset = reinterpret_cast<uintptr_t>(devicePointer) - reinterpret_cast<uintptr_t>(it->second.raw);
+    std::memcpy(handle, &h, sizeof(h));
+    std::memcpy(static_cast<uint8_t *>(handle) + sizeof(h), &offset, sizeof(offset));
+    return rebind_current();
+}
+
+libreCudaStatus_t libreCuIpcOpenMemHandle(void **pDevicePointer, const void *handle) {
+    LIBRECUDA_VALIDATE(pDevicePointer != nullptr && handle != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LCU_ENSURE_CTX();
+    LIBRECUDA_ERR_PROPAGATE(bind(globals().current));
+    cudaIpcMemHandle_t h;
+    uint64_t offset = 0;
+    std::memcpy(&h, handle, sizeof(h));
+    std::memcpy(&offset, static_cast<const uint8_t *>(handle) + sizeof(h), sizeof(offset));
+    void *raw = nullptr;
+    LCU_CUDA(cudaIpcOpenMemHandle(&raw, h, cudaIpcMemLazyEnablePeerAccess));
+    void *p = static_cast<uint8_t *>(raw) + offset;
+    // size unknown on this side: register the page that holds the pointer so classification sees device memory;
+    // the CUDA driver answers for the rest of the range
+    globals().allocations[reinterpret_cast<uintptr_t>(p)] = Allocation{raw, 4096, globals().current->device->ordinal, false, true};
+    *pDevicePointer = p;
+    LIBRECUDA_SUCCEED();
+}
+
+libreCudaStatus_t libreCuIpcCloseMemHandle(void *devicePointer) {
+    LIBRECUDA_VALIDATE(devicePointer != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    auto &allocs = globals().allocations;
+    auto it = allocs.find(reinterpret_cast<uintptr_t>(devicePointer));
+    LIBRECUDA_VALIDATE(it != allocs.end() && it->second.ipc, LIBRECUDA_ERROR_INVALID_VALUE);
+    LCU_CUDA(cudaSetDevice(it->second.device));
+    void *raw = it->second.raw;
+    allocs.erase(it);
+    LCU_CUDA(cudaIpcCloseMemHandle(raw));
+    return rebind_current();
+}

@@ -1,0 +1,400 @@
+// Stream / event ordering layer and the stream-recorded operations (copies, memset, launches).
+//
+// Semantics kept from the reference's NvCommandQueue (driverapi/src/cmdqueue.cpp):
+//  * operations are recorded and reach the GPU at Commence (:200-218, :821-868); Await blocks until the
+//    submitted work is complete (:272-277, :334-357);
+//  * async=false orders an operation after everything recorded before it, async=true lets it overlap
+//    earlier operations of the same stream (:480-487, :715-727);
+//  * events are timestamped markers in the stream (:896-955).
+// What changed: ordering is resolved on the GPU.  An ordered operation runs on the stream's main CUDA
+// stream; an async operation is forked onto one of a few side streams that start at the last ordered point,
+// and the next ordered operation (or event, or Await) joins them back with CUDA events.  Copies that touch
+// host memory go to the copy engines, device-to-device copies to this library's copy kernel, and neither
+// switch costs a CPU round trip (the reference replays every compute<->DMA switch with a CPU wait, :826-844).
+#include <chrono>
+#include <cstdlib>
+#include <cstring>
+#include <thread>
+
+#include "internal.h"
+
+using namespace lcu;
+
+namespace lcu {
+
+libreCudaStatus_t record(LibreCUstream stream, Command &&cmd) {
+    stream->pending.push_back(std::move(cmd));
+    LIBRECUDA_SUCCEED();
+}
+
+// Host-side wait in the style chosen at context creation (reference cmdqueue.cpp:337-355).
+template <typename QueryFn, typename BlockFn>
+static libreCudaStatus_t host_wait(LibreCUcontext ctx, QueryFn query, BlockFn block) {
+    const int flags = ctx ? ctx->flags : 0;
+    if (flags & CU_CTX_SCHED_BLOCKING_SYNC) {
+        LCU_CUDA(block());
+        LIBRECUDA_SUCCEED();
+    }
+    const bool yield = !(flags & CU_CTX_SCHED_SPIN) && (flags & CU_CTX_SCHED_YIELD);
+    for (;;) {
+        cudaError_t q = query();
+        if (q == cudaSuccess) LIBRECUDA_SUCCEED();
+        if (q != cudaErrorNotReady) LCU_CUDA(q);
+        if (yield) std::this_thread::yield();
+    }
+}
+
+libreCudaStatus_t host_wait_stream(LibreCUcontext ctx, cudaStream_t s) {
+    return host_wait(ctx, [&] { return cudaStreamQuery(s); }, [&] { return cudaStreamSynchronize(s); });
+}
+
+libreCudaStatus_t host_wait_event(LibreCUcontext ctx, cudaEvent_t e) {
+    return host_wait(ctx, [&] { return cudaEventQuery(e); }, [&] { return cudaEventSynchronize(e); });
+}
+
+static libreCudaStatus_t join_sides(LibreCUstream st) {
+    for (int i = 0; i < kSideLanes; ++i) {
+        if (!st->side_dirty[i]) continue;
+        LCU_CUDA(cudaEventRecord(st->side_done[i], st->side[i]));
+        LCU_CUDA(cudaStreamWaitEvent(st->main, st->side_done[i], 0));
+        st->side_dirty[i] = false;
+    }
+    LIBRECUDA_SUCCEED();
+}
+
+// Lane an operation runs on: the main stream after a join for ordered operations, a side stream forked
+// from the main stream's current tail for async ones.
+static libreCudaStatus_t pick_lane(LibreCUstream st, bool async, cudaStream_t *lane) {
+    if (!async) {
+        LIBRECUDA_ERR_PROPAGATE(join_sides(st));
+        *lane = st->main;
+        LIBRECUDA_SUCCEED();
+    }
+    const int i = st->next_side;
+    st->next_side = (i + 1) % kSideLanes;
+    if (st->side[i] == nullptr) {
+        LCU_CUDA(cudaStreamCreateWithFlags(&st->side[i], cudaStreamNonBlocking));
+        LCU_CUDA(cudaEventCreateWithFlags(&st->side_done[i], cudaEventDisableTiming));
+    }
+    LCU_CUDA(cudaEventRecord(st->fork, st->main));
+    LCU_CUDA(cudaStreamWaitEvent(st->side[i], st->fork, 0));
+    st->side_dirty[i] = true;
+    *lane = st->side[i];
+    LIBRECUDA_SUCCEED();
+}
+
+static libreCudaStatus_t submit(LibreCUstream st, Command &c) {
+    cudaStream_t lane = nullptr;
+    switch (c.kind) {
+        case Command::CopyKernel:
+            LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
+            LCU_LCB(lcb_copy_d2d(c.dst, c.src, c.bytes, lane));
+            break;
+        case Command::CopyEngine:
+            LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
+            LCU_CUDA(cudaMemcpyAsync(c.dst, c.src, c.bytes, c.copy_kind, lane));
+            break;
+        case Command::Memset:
+            LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
+            LCU_LCB(lcb_memset_ex(c.dst, c.value, c.elem, c.bytes / (size_t)c.elem, 0, 0, lane));
+            break;
+        case Command::AllToAllPush:
+            LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
+            LCU_LCB(lcb_alltoall_push(c.peers.data(), c.src, c.bytes, (int)c.peers.size(), c.rank, lane));
+            break;
+        case Command::Launch: {
+            LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
+            LibreCUFunction f = c.fn;
+            std::vector<void *> argv(f->param_size.size());
+            for (size_t i = 0; i < argv.size(); ++i) argv[i] = c.params.data() + f->param_offset[i];
+            LCU_CU(driver()->LaunchKernel(f->fn, c.grid[0], c.grid[1], c.grid[2], c.block[0], c.block[1], c.block[2],
+                                          c.smem, lane, argv.empty() ? nullptr : argv.data(), nullptr));
+            break;
+        }
+        case Command::EventRecord: {
+            LIBRECUDA_ERR_PROPAGATE(join_sides(st));
+            LibreCUEvent e = c.event;
+            if (e->ev != nullptr && e->device != st->ctx->device->ordinal) {
+                (void)cudaEventDestroy(e->ev);
+                e->ev = nullptr;
+            }
+            if (e->ev == nullptr) {
+                LCU_CUDA(cudaEventCreate(&e->ev));
+                e->device = st->ctx->device->ordinal;
+            }
+            LCU_CUDA(cudaEventRecord(e->ev, st->main));
+            e->state = LibreCUEvent_::Submitted;
+            break;
+        }
+        case Command::WaitEvent:
+            // later operations fork from / run on the main stream, so they all observe the wait
+            LCU_CUDA(cudaStreamWaitEvent(st->main, c.event->ev, 0));
+            break;
+    }
+    LIBRECUDA_SUCCEED();
+}
+
+libreCudaStatus_t commence(LibreCUstream st) {
+    LIBRECUDA_ERR_PROPAGATE(bind(st->ctx));
+    // a wait on an event whose record has not been submitted anywhere cannot be honoured: refuse the whole
+    // batch before anything is submitted
+    for (size_t i = 0; i < st->pending.size(); ++i) {
+        const Command &c = st->pending[i];
+        if (c.kind != Command::WaitEvent) continue;
+        LibreCUEvent e = c.event;
+        if (e->state == LibreCUEvent_::Submitted) continue;
+        bool earlier_here = false;
+        for (size_t j = 0; j < i; ++j)
+            if (st->pending[j].kind == Command::EventRecord && st->pending[j].event == e) earlier_here = true;
+        LIBRECUDA_VALIDATE(earlier_here, LIBRECUDA_ERROR_NOT_READY);
+    }
+    std::vector<Command> batch;
+    batch.swap(st->pending);
+    for (Command &c : batch) LIBRECUDA_ERR_PROPAGATE(submit(st, c));
+    LibreCUcontext cur = globals().current;
+    if (cur != nullptr && cur != st->ctx) LIBRECUDA_ERR_PROPAGATE(bind(cur));
+    LIBRECUDA_SUCCEED();
+}
+
+}  // namespace lcu
+
+// ---- streams ----------------------------------------------------------------------------------------------
+
+libreCudaStatus_t libreCuStreamCreate(LibreCUstream *pStreamOut, uint32_t flags) {
+    (void)flags;
+    LIBRECUDA_VALIDATE(pStreamOut != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LCU_ENSURE_CTX();
+    LibreCUcontext ctx = globals().current;
+    LIBRECUDA_ERR_PROPAGATE(bind(ctx));
+    auto st = std::make_unique<LibreCUstream_>();
+    st->ctx = ctx;
+    LCU_CUDA(cudaStreamCreateWithFlags(&st->main, cudaStreamNonBlocking));
+    LCU_CUDA(cudaEventCreateWithFlags(&st->fork, cudaEventDisableTiming));
+    *pStreamOut = st.release();
+    LIBRECUDA_SUCCEED();
+}
+
+libreCudaStatus_t libreCuStreamDestroy(LibreCUstream stream) {
+    LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    if (cudaSetDevice(stream->ctx->device->ordinal) == cudaSuccess) {
+        for (int i = 0; i < kSideLanes; ++i) {
+            if (stream->side[i]) {
+                (void)cudaStreamSynchronize(stream->side[i]);
+                (void)cudaStreamDestroy(stream->side[i]);
+                (void)cudaEventDestroy(stream->side_done[i]);
+            }
+        }
+        (void)cudaStreamSynchronize(stream->main);
+        (void)cudaStreamDestroy(stream->main);
+        (void)cudaEventDestroy(stream->fork);
+    }
+    (void)cudaGetLastError();
+    LibreCUcontext cur = globals().current;
+    delete stream;
+    if (cur != nullptr) (void)cudaSetDevice(cur->device->ordinal);
+    LIBRECUDA_SUCCEED();
+}
+
+libreCudaStatus_t libreCuStreamCommence(LibreCUstream stream) {
+    LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    return commence(stream);
+}
+
+libreCudaStatus_t libreCuStreamAwait(LibreCUstream stream) {
+    LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_ERR_PROPAGATE(bind(stream->ctx));
+    LIBRECUDA_ERR_PROPAGATE(join_sides(stream));
+    LIBRECUDA_ERR_PROPAGATE(host_wait_stream(stream->ctx, stream->main));
+    LibreCUcontext cur = globals().current;
+    if (cur != nullptr && cur != stream->ctx) LIBRECUDA_ERR_PROPAGATE(bind(cur));
+    LIBRECUDA_SUCCEED();
+}
+
+libreCudaStatus_t libreCuStreamGetNativeHandle(void **pNativeStreamOut, LibreCUstream stream) {
+    LIBRECUDA_VALIDATE(pNativeStreamOut != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    *pNativeStreamOut = stream->main;
+    LIBRECUDA_SUCCEED();
+}
+
+// ---- copies -----------------------------------------------------------------------------------------------
+
+static libreCudaStatus_t record_copy(void *dst, const void *src, size_t n, LibreCUstream stream, bool async,
+                                     PtrClass dc, PtrClass sc) {
+    if (n == 0) LIBRECUDA_SUCCEED();
+    Command c;
+    c.async = async;
+    c.dst = dst;
+    c.src = src;
+    c.bytes = n;
+    if (dc == PtrClass::Device && sc == PtrClass::Device) {
+        c.kind = Command::CopyKernel;  // reference: memcpyD2D, memcopy.cpp:77
+    } else {
+        c.kind = Command::CopyEngine;  // reference: gpuMemcpy, cmdqueue.cpp:732
+        c.copy_kind = dc == PtrClass::Device ? cudaMemcpyHostToDevice
+                      : sc == PtrClass::Device ? cudaMemcpyDeviceToHost
+                                               : cudaMemcpyHostToHost;
+    }
+    return record(stream, std::move(c));
+}
+
+libreCudaStatus_t libreCuMemCpy(void *dst, void *src, size_t byteCount, LibreCUstream stream, bool async) {
+    LIBRECUDA_VALIDATE(dst != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(src != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LCU_ENSURE_CTX();
+    return record_copy(dst, src, byteCount, stream, async, classify(dst), classify(src));
+}
+
+static libreCudaStatus_t directional(void *dst, const void *src, size_t n, LibreCUstream stream, bool async,
+                                     PtrClass want_dst, PtrClass want_src) {
+    LIBRECUDA_VALIDATE(dst != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(src != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LCU_ENSURE_CTX();
+    const PtrClass dc = classify(dst), sc = classify(src);
+    LIBRECUDA_VALIDATE(dc == want_dst, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(sc == want_src, LIBRECUDA_ERROR_INVALID_VALUE);
+    return record_copy(dst, src, n, stream, async, dc, sc);
+}
+
+libreCudaStatus_t libreCuMemcpyHtoD(void *d, const void *s, size_t n, LibreCUstream st) {
+    return directional(d, s, n, st, false, PtrClass::Device, PtrClass::Host);
+}
+libreCudaStatus_t libreCuMemcpyHtoDAsync(void *d, const void *s, size_t n, LibreCUstream st) {
+    return directional(d, s, n, st, true, PtrClass::Device, PtrClass::Host);
+}
+libreCudaStatus_t libreCuMemcpyDtoH(void *d, const void *s, size_t n, LibreCUstream st) {
+    return directional(d, s, n, st, false, PtrClass::Host, PtrClass::Device);
+}
+libreCudaStatus_t libreCuMemcpyDtoHAsync(void *d, const void *s, size_t n, LibreCUstream st) {
+    return directional(d, s, n, st, true, PtrClass::Host, PtrClass::Device);
+}
+libreCudaStatus_t libreCuMemcpyDtoD(void *d, const void *s, size_t n, LibreCUstream st) {
+    return directional(d, s, n, st, false, PtrClass::Device, PtrClass::Device);
+}
+libreCudaStatus_t libreCuMemcpyDtoDAsync(void *d, const void *s, size_t n, LibreCUstream st) {
+    return directional(d, s, n, st, true, PtrClass::Device, PtrClass::Device);
+}
+
+libreCudaStatus_t libreCuMemcpyPeer(void *dstDevice, const void *srcDevice, size_t byteCount, LibreCUstream stream,
+                                    bool async) {
+    return directional(dstDevice, srcDevice, byteCount, stream, async, PtrClass::Device, PtrClass::Device);
+}
+
+// ---- memset -----------------------------------------------------------------------------------------------
+
+static libreCudaStatus_t record_memset(void *dst, unsigned int value, int elem, size_t count, LibreCUstream stream,
+                                       bool async) {
+    LIBRECUDA_VALIDATE(dst != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LCU_ENSURE_CTX();
+    LIBRECUDA_VALIDATE((reinterpret_cast<uintptr_t>(dst) & (uintptr_t)(elem - 1)) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(classify(dst) == PtrClass::Device, LIBRECUDA_ERROR_INVALID_VALUE);
+    if (count == 0) LIBRECUDA_SUCCEED();
+    Command c;
+    c.kind = Command::Memset;
+    c.async = async;
+    c.dst = dst;
+    c.value = value;
+    c.elem = elem;
+    c.bytes = count * (size_t)elem;
+    return record(stream, std::move(c));
+}
+
+libreCudaStatus_t libreCuMemsetD8(void *d, unsigned char v, size_t n, LibreCUstream st) { return record_memset(d, v, 1, n, st, false); }
+libreCudaStatus_t libreCuMemsetD8Async(void *d, unsigned char v, size_t n, LibreCUstream st) { return record_memset(d, v, 1, n, st, true); }
+libreCudaStatus_t libreCuMemsetD16(void *d, unsigned short v, size_t n, LibreCUstream st) { return record_memset(d, v, 2, n, st, false); }
+libreCudaStatus_t libreCuMemsetD16Async(void *d, unsigned short v, size_t n, LibreCUstream st) { return record_memset(d, v, 2, n, st, true); }
+libreCudaStatus_t libreCuMemsetD32(void *d, unsigned int v, size_t n, LibreCUstream st) { return record_memset(d, v, 4, n, st, false); }
+libreCudaStatus_t libreCuMemsetD32Async(void *d, unsigned int v, size_t n, LibreCUstream st) { return record_memset(d, v, 4, n, st, true); }
+
+// ---- events -----------------------------------------------------------------------------------------------
+
+libreCudaStatus_t libreCuEventCreate(LibreCUEvent *pEventOut, uint32_t flags) {
+    (void)flags;
+    LIBRECUDA_VALIDATE(pEventOut != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    *pEventOut = new LibreCUEvent_();
+    LIBRECUDA_SUCCEED();
+}
+
+libreCudaStatus_t libreCuEventRecord(LibreCUEvent event, LibreCUstream stream) {
+    LIBRECUDA_VALIDATE(event != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    event->stream = stream;
+    event->ctx = stream->ctx;
+    event->state = LibreCUEvent_::Pending;
+    Command c;
+    c.kind = Command::EventRecord;
+    c.event = event;
+    return record(stream, std::move(c));
+}
+
+libreCudaStatus_t libreCuEventSynchronize(LibreCUEvent event) {
+    LIBRECUDA_VALIDATE(event != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(event->state != LibreCUEvent_::Never, LIBRECUDA_ERROR_INVALID_VALUE);  // reference librecuda.cpp:1633
+    // recorded but its stream never commenced: the reference would spin forever (cmdqueue.cpp:928-940)
+    LIBRECUDA_VALIDATE(event->state == LibreCUEvent_::Submitted, LIBRECUDA_ERROR_NOT_READY);
+    return host_wait_event(event->ctx, event->ev);
+}
+
+libreCudaStatus_t libreCuEventQuery(LibreCUEvent event) {
+    LIBRECUDA_VALIDATE(event != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(event->state != LibreCUEvent_::Never, LIBRECUDA_ERROR_INVALID_VALUE);
+    if (event->state != LibreCUEvent_::Submitted) LIBRECUDA_FAIL(LIBRECUDA_ERROR_NOT_READY);
+    cudaError_t q = cudaEventQuery(event->ev);
+    if (q == cudaErrorNotReady) LIBRECUDA_FAIL(LIBRECUDA_ERROR_NOT_READY);
+    LCU_CUDA(q);
+    LIBRECUDA_SUCCEED();
+}
+
+libreCudaStatus_t libreCuEventElapsedTime(float *pMillisecondsOut, LibreCUEvent start, LibreCUEvent end) {
+    LIBRECUDA_VALIDATE(pMillisecondsOut != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(start != nullptr && end != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(start->state != LibreCUEvent_::Never && end->state != LibreCUEvent_::Never, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(start->stream == end->stream, LIBRECUDA_ERROR_INVALID_VALUE);  // reference librecuda.cpp:1641-1643
+    if (start->state != LibreCUEvent_::Submitted || end->state != LibreCUEvent_::Submitted) LIBRECUDA_FAIL(LIBRECUDA_ERROR_NOT_READY);
+    cudaError_t e = cudaEventElapsedTime(pMillisecondsOut, start->ev, end->ev);
+    if (e == cudaErrorNotReady) {
+        (void)cudaGetLastError();
+        LIBRECUDA_FAIL(LIBRECUDA_ERROR_NOT_READY);
+    }
+    LCU_CUDA(e);
+    LIBRECUDA_SUCCEED();
+}
+
+libreCudaStatus_t libreCuEventGetTimestamp(uint64_t *pNanosecondsOut, LibreCUEvent event) {
+    LIBRECUDA_VALIDATE(pNanosecondsOut != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(event != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(event->state != LibreCUEvent_::Never, LIBRECUDA_ERROR_INVALID_VALUE);
+    if (event->state != LibreCUEvent_::Submitted) LIBRECUDA_FAIL(LIBRECUDA_ERROR_NOT_READY);
+    float ms = 0.f;
+    cudaError_t e = cudaEventElapsedTime(&ms, event->ctx->epoch, event->ev);
+    if (e == cudaErrorNotReady) {
+        (void)cudaGetLastError();
+        LIBRECUDA_FAIL(LIBRECUDA_ERROR_NOT_READY);
+    }
+    LCU_CUDA(e);
+    *pNanosecondsOut = (uint64_t)((double)ms * 1.0e6);
+    LIBRECUDA_SUCCEED();
+}
+
+libreCudaStatus_t libreCuEventDestroy(LibreCUEvent event) {
+    LIBRECUDA_VALIDATE(event != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    if (event->ev) {
+        (void)cudaEventDestroy(event->ev);
+        (void)cudaGetLastError();
+    }
+    delete event;
+    LIBRECUDA_SUCCEED();
+}
+
+libreCudaStatus_t libreCuStreamWaitEvent(LibreCUstream stream, LibreCUEvent event) {
+    LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(event != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE(event->state != LibreCUEvent_::Never, LIBRECUDA_ERROR_INVALID_VALUE);
+    Command c;
+    c.kind = Command::WaitEvent;
+    c.event = event;
+    return record(stream, std::move(c));
+}

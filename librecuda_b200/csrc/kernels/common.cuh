@@ -1,0 +1,159 @@
+// Shared device helpers for the sm_100a data-movement kernels: streaming vector accesses, the
+// non-multicast bulk-copy (TMA) primitives with bounded mbarrier waits, and launch plumbing.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace lcb {
+
+// Bit 0 of the sticky per-device error word (defined beside the bulk-copy ring that sets it):
+// an mbarrier wait gave up.
+constexpr unsigned int kErrMbarrierTimeout = 1u;
+
+// Tunables reachable through lcb_tune() (for sweeps; the defaults are the shipped configuration).
+struct Tuning {
+    int copy_vec_threads;   // threads per CTA of the vector copy kernel
+    int copy_vec_unroll;    // 16-byte vectors in flight per thread
+    int copy_vec_ctas_sm;   // resident CTAs per SM assumed when sizing the persistent grid
+    int copy_cache_mode;    // 0: ld.cs/st.cs   1: default caching   2: L1::no_allocate
+    int tma_chunk;          // bytes per bulk copy
+    int tma_stages;         // ring depth
+    int tma_lookahead;      // loads in flight ahead of the store
+    int tma_ctas_sm;        // CTAs per SM of the bulk ring kernels
+    int tma_cache_hint;     // 0: none  1: evict_first policy on loads and stores
+    int auto_tma_min_bytes; // LCB_COPY_AUTO uses the bulk ring from this size on (mutually aligned only)
+    int memset_path;        // 0 auto, 1 vector, 2 bulk
+    int memset_unroll;
+    int memset_threads;
+    int memset_ctas_sm;
+};
+Tuning &tuning();
+
+int sm_count();            // SMs of the current device (cached per device)
+int check_launch();        // cudaGetLastError() as int
+
+// ---------------------------------------------------------------------------------------------
+// streaming 16-byte accesses
+// ---------------------------------------------------------------------------------------------
+template <int MODE>
+__device__ __forceinline__ uint4 ld_stream(const uint4 *p) {
+    uint4 v;
+    if (MODE == 0) {
+        asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    } else if (MODE == 1) {
+        asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    } else {
+        asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    }
+    return v;
+}
+
+template <int MODE>
+__device__ __forceinline__ void st_stream(uint4 *p, uint4 v) {
+    if (MODE == 0) {
+        asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};"
+                     :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+    } else if (MODE == 1) {
+        asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};"
+                     :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+    } else {
+        asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};"
+                     :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// bulk-copy (TMA, untiled) primitives.  Only the non-multicast forms are used anywhere in this library.
+// Both addresses of a bulk copy are 16-byte aligned and the size is a multiple of 16.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+
+// Bounded wait for the phase with parity `parity`.  Returns false when it gives up.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    constexpr uint32_t kMaxTries = 1u << 22;  // each try may itself suspend for a hardware-chosen time
+    for (uint32_t i = 0; i < kMaxTries; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (i > 4096) __nanosleep(64);
+    }
+    return false;
+}
+
+template <bool HINT>
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar,
+                                         uint64_t policy) {
+    if (HINT) {
+        asm volatile(
+            "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+            :: "r"(dst_smem), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
+    } else {
+        asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     :: "r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+    }
+}
+
+template <bool HINT>
+__device__ __forceinline__ void bulk_s2g(void *dst, uint32_t src_smem, uint32_t bytes, uint64_t policy) {
+    if (HINT) {
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;"
+                     :: "l"(dst), "r"(src_smem), "r"(bytes), "l"(policy) : "memory");
+    } else {
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                     :: "l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+    }
+}
+
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(N) : "memory");
+}
+
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
+__device__ __forceinline__ void fence_generic_to_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// splitmix64 finaliser; shared by the seeded generator and the checksum.
+__host__ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+constexpr uint64_t kGolden = 0x9E3779B97F4A7C15ull;
+
+}  // namespace lcb

@@ -1,0 +1,452 @@
+// Device-to-device copy kernels for sm_100a and their C-ABI launchers.
+//
+// Replaces the reference's three-kernel split (memcpyD2D, driverapi/src/memcopy.cpp:77-158, launching
+// memcpyKernelHighBW / LowLatency / Trailing, driverapi/kernels/memcpy/memcpy.cu:5-27) with ONE launch
+// per copy that handles any size and any alignment:
+//
+//   dst:  [ head < 16 B ][ body: nvec 16-byte vectors, dst 16-byte aligned ][ tail < 16 B ]
+//
+//  * copy_vec_kernel    persistent grid, each lane keeps U 16-byte loads in flight before storing.
+//                       If src is not congruent to dst mod 16 the lanes load ALIGNED source vectors and
+//                       rebuild each output vector from their own vector and their right neighbour's,
+//                       fetched with one warp shuffle per word (lane 0 supplies the first vector of the
+//                       next row), then a funnel shift for the sub-word part.  No misaligned access is
+//                       ever issued; DRAM traffic stays at the algorithmic 2 bytes per byte copied.
+//  * copy_tma_kernel    for mutually aligned spans: one thread per CTA drives a ring of bulk copies
+//                       (cp.async.bulk global->shared with mbarrier complete_tx, then shared->global in
+//                       bulk groups).  Non-multicast forms only, so the same kernel is usable with a peer
+//                       GPU's memory on either side.
+//  * alltoall_push_kernel  one launch that stores every chunk of a send buffer into the matching slot of
+//                       every peer's receive buffer (the copy fused with the exchange).
+#include "common.cuh"
+#include "lcb200_kernels.h"
+
+namespace lcb {
+
+// Sticky per-device error word, read and cleared by lcb_device_error_word().
+__device__ unsigned int g_error_word = 0;
+
+// ---------------------------------------------------------------------------------------------
+// vector path
+// ---------------------------------------------------------------------------------------------
+
+// Output vector from two consecutive aligned source vectors when the source stream starts
+// s = 4*SW + sb bytes into `a` (sb8 = 8*sb).
+template <int SW>
+__device__ __forceinline__ uint4 realign(const uint4 &a, const uint4 &b, int sb8) {
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint4 o;
+    o.x = __funnelshift_r(w[SW + 0], w[SW + 1], sb8);
+    o.y = __funnelshift_r(w[SW + 1], w[SW + 2], sb8);
+    o.z = __funnelshift_r(w[SW + 2], w[SW + 3], sb8);
+    o.w = __funnelshift_r(w[SW + 3], w[SW + 4], sb8);
+    return o;
+}
+
+struct Edges {            // the < 16-byte pieces either side of the vector body
+    uint8_t *dst;         // original dst
+    const uint8_t *src;   // original src
+    int head;             // bytes before the body
+    int tail;             // bytes after the body
+    size_t tail_off;      // offset of the tail from dst / src
+};
+
+__device__ __forceinline__ void copy_edges(const Edges &e, int t) {
+    // two different warps so head and tail go out together
+    if (t < e.head) e.dst[t] = e.src[t];
+    int u = t - 32;
+    if (u >= 0 && u < e.tail) e.dst[e.tail_off + u] = e.src[e.tail_off + u];
+}
+
+// SW < 0: src and dst congruent mod 16 (srcv is the source body itself).
+// SW in 0..3: srcv is the source body rounded DOWN to 16 bytes; output vector j is bytes
+// [16 j + s, 16 j + s + 16) of the srcv stream with s = 4 SW + sb8 / 8, 1 <= s <= 15.
+template <int SW, int U, int MODE>
+__global__ void __launch_bounds__(512) copy_vec_kernel(uint4 *__restrict__ dstv, const uint4 *__restrict__ srcv,
+                                                       size_t nvec, int sb8, Edges e) {
+    const int lane = threadIdx.x & 31;
+    const size_t warps_total = (size_t)gridDim.x * (blockDim.x >> 5);
+    const size_t gwarp = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    constexpr size_t TILE = (size_t)U * 32;  // vectors per warp per iteration
+    const size_t ntiles = (nvec + TILE - 1) / TILE;
+
+    if (blockIdx.x == 0) copy_edges(e, threadIdx.x);
+
+    for (size_t t = gwarp; t < ntiles; t += warps_total) {
+        const size_t base = t * TILE;
+        uint4 v[U];
+        if (base + TILE <= nvec) {  // full tile: no guards
+#pragma unroll
+            for (int u = 0; u < U; ++u) v[u] = ld_stream<MODE>(srcv + base + u * 32 + lane);
+            if (SW < 0) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) st_stream<MODE>(dstv + base + u * 32 + lane, v[u]);
+            } else {
+                uint4 extra = make_uint4(0, 0, 0, 0);
+                if (lane == 0) extra = ld_stream<MODE>(srcv + base + TILE);
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    // every lane needs the vector one to its right; lane 31's neighbour is lane 0's next row
+                    uint4 give = v[u];
+                    if (lane == 0) give = (u + 1 < U) ? v[(u + 1 < U) ? u + 1 : u] : extra;
+                    uint4 nxt;
+                    const int from = (lane + 1) & 31;
+                    nxt.x = __shfl_sync(0xffffffffu, give.x, from);
+                    nxt.y = __shfl_sync(0xffffffffu, give.y, from);
+                    nxt.z = __shfl_sync(0xffffffffu, give.z, from);
+                    nxt.w = __shfl_sync(0xffffffffu, give.w, from);
+                    st_stream<MODE>(dstv + base + u * 32 + lane, realign<(SW < 0 ? 0 : SW)>(v[u], nxt, sb8));
+                }
+            }
+        } else {  // last, partial tile
+            // realign mode also needs source vector index nvec (it holds the last bytes of the body)
+            const size_t src_limit = (SW < 0) ? nvec : nvec + 1;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const size_t j = base + u * 32 + lane;
+                v[u] = (j < src_limit) ? ld_stream<MODE>(srcv + j) : make_uint4(0, 0, 0, 0);
+            }
+            if (SW < 0) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const size_t j = base + u * 32 + lane;
+                    if (j < nvec) st_stream<MODE>(dstv + j, v[u]);
+                }
+            } else {
+                uint4 extra = make_uint4(0, 0, 0, 0);
+                if (lane == 0 && base + TILE < src_limit) extra = ld_stream<MODE>(srcv + base + TILE);
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    uint4 give = v[u];
+                    if (lane == 0) give = (u + 1 < U) ? v[(u + 1 < U) ? u + 1 : u] : extra;
+                    uint4 nxt;
+                    const int from = (lane + 1) & 31;
+                    nxt.x = __shfl_sync(0xffffffffu, give.x, from);
+                    nxt.y = __shfl_sync(0xffffffffu, give.y, from);
+                    nxt.z = __shfl_sync(0xffffffffu, give.z, from);
+                    nxt.w = __shfl_sync(0xffffffffu, give.w, from);
+                    const size_t j = base + u * 32 + lane;
+                    if (j < nvec) st_stream<MODE>(dstv + j, realign<(SW < 0 ? 0 : SW)>(v[u], nxt, sb8));
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// bulk-copy ring
+// ---------------------------------------------------------------------------------------------
+
+// One CTA = one warp; lane 0 runs the ring, the other lanes of CTA 0 copy the edge bytes.
+// Chunk c of the body (chunk bytes each, the last one shorter) belongs to CTA c % gridDim.x.
+// S stages, L loads in flight ahead of the store front.  Stage reuse: before loading chunk k+L into
+// its stage, the bulk store that last read that stage (chunk k+L-S) must have finished reading
+// shared memory, i.e. at most S-L younger store groups may still be pending.
+template <int S, int L, bool HINT>
+__global__ void __launch_bounds__(32) copy_tma_kernel(uint8_t *__restrict__ dst, const uint8_t *__restrict__ src,
+                                                      size_t body, uint32_t chunk, Edges e) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    static_assert(L >= 1 && L < S, "need at least one stage of slack between loads and stores");
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)S * chunk);
+
+    if (blockIdx.x == 0 && threadIdx.x != 0) {
+        // lanes 1..15 -> head bytes, lanes 16..31 -> tail bytes
+        const int t = threadIdx.x;
+        if (t < 16) {
+            if (t - 1 < e.head) e.dst[t - 1] = e.src[t - 1];
+        } else if (t - 16 < e.tail) {
+            e.dst[e.tail_off + (t - 16)] = e.src[e.tail_off + (t - 16)];
+        }
+        // (head and tail are < 16 by construction, 15 lanes each are enough)
+    }
+    if (threadIdx.x != 0) return;
+
+    const size_t nchunks = (body + chunk - 1) / chunk;
+    if ((size_t)blockIdx.x >= nchunks) return;
+    const size_t n_my = (nchunks - blockIdx.x + gridDim.x - 1) / gridDim.x;
+
+    const uint32_t smem_base = smem_addr(smem);
+    const uint32_t bar_base = smem_addr(bars);
+    for (int s = 0; s < S; ++s) mbar_init(bar_base + 8 * s, 1);
+    mbar_init_fence();
+
+    uint64_t pol = 0;
+    if (HINT) pol = policy_evict_first();
+
+    auto chunk_off = [&](size_t k) { return ((size_t)blockIdx.x + k * gridDim.x) * (size_t)chunk; };
+    auto chunk_len = [&](size_t k) {
+        const size_t off = chunk_off(k);
+        const size_t rem = body - off;
+        return (uint32_t)(rem < chunk ? rem : chunk);
+    };
+    auto issue_load = [&](size_t k) {
+        const int s = (int)(k % S);
+        const uint32_t len = chunk_len(k);
+        mbar_expect_tx(bar_base + 8 * s, len);
+        bulk_g2s<HINT>(smem_base + s * chunk, src + chunk_off(k), len, bar_base + 8 * s, pol);
+    };
+
+    size_t issued = 0;
+    for (; issued < (size_t)L && issued < n_my; ++issued) issue_load(issued);
+
+    bool ok = true;
+    size_t k = 0;
+    for (; k < n_my; ++k) {
+        const int s = (int)(k % S);
+        const uint32_t parity = (uint32_t)((k / S) & 1);
+        if (!mbar_wait_bounded(bar_base + 8 * s, parity)) { ok = false; break; }
+        bulk_s2g<HINT>(dst + chunk_off(k), smem_base + s * chunk, chunk_len(k), pol);
+        bulk_commit();
+        if (issued < n_my) {
+            if (issued >= (size_t)S) bulk_wait_read<S - L>();
+            issue_load(issued);
+            ++issued;
+        }
+    }
+    if (!ok) {
+        atomicOr(&g_error_word, kErrMbarrierTimeout);
+        // loads already issued still target our shared memory: give each one more bounded wait
+        for (size_t j = k; j < issued; ++j) mbar_wait_bounded(bar_base + 8 * (int)(j % S), (uint32_t)((j / S) & 1));
+    }
+    bulk_wait_all();
+}
+
+// ---------------------------------------------------------------------------------------------
+// all-to-all push
+// ---------------------------------------------------------------------------------------------
+struct PeerPtrs {
+    uint4 *recv[16];
+};
+
+// CTA b serves peer (rank + 1 + b % n) % n, so consecutive CTAs feed different NVLink destinations and
+// every link is busy from the first wave on; within a peer the CTAs stride over warp tiles.
+template <int U, int MODE>
+__global__ void __launch_bounds__(512) alltoall_push_kernel(PeerPtrs peers, const uint4 *__restrict__ send,
+                                                            size_t chunk_vec, int n, int rank) {
+    const int lane = threadIdx.x & 31;
+    const int slot = blockIdx.x % n;
+    const int peer = (rank + 1 + slot) % n;
+    const size_t ctas_per_peer = gridDim.x / n;  // grid is a multiple of n
+    const size_t cta_in_peer = blockIdx.x / n;
+    const size_t warps_total = ctas_per_peer * (blockDim.x >> 5);
+    const size_t gwarp = cta_in_peer * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    constexpr size_t TILE = (size_t)U * 32;
+    const size_t ntiles = (chunk_vec + TILE - 1) / TILE;
+    const uint4 *s = send + (size_t)peer * chunk_vec;
+    uint4 *d = peers.recv[peer] + (size_t)rank * chunk_vec;
+    for (size_t t = gwarp; t < ntiles; t += warps_total) {
+        const size_t base = t * TILE;
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const size_t j = base + u * 32 + lane;
+            v[u] = (j < chunk_vec) ? ld_stream<MODE>(s + j) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const size_t j = base + u * 32 + lane;
+            if (j < chunk_vec) st_stream<1>(d + j, v[u]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+struct Split {
+    Edges e;
+    uint4 *dstv;
+    const uint8_t *src_body;
+    size_t nvec;
+};
+
+Split split_copy(void *dst, const void *src, size_t bytes) {
+    Split sp;
+    uint8_t *d = static_cast<uint8_t *>(dst);
+    const uint8_t *s = static_cast<const uint8_t *>(src);
+    size_t head = (16 - (reinterpret_cast<uintptr_t>(d) & 15)) & 15;
+    if (head > bytes) head = bytes;
+    const size_t nvec = (bytes - head) / 16;
+    const size_t tail = bytes - head - nvec * 16;
+    sp.e.dst = d;
+    sp.e.src = s;
+    sp.e.head = (int)head;
+    sp.e.tail = (int)tail;
+    sp.e.tail_off = head + nvec * 16;
+    sp.dstv = reinterpret_cast<uint4 *>(d + head);
+    sp.src_body = s + head;
+    sp.nvec = nvec;
+    return sp;
+}
+
+template <int SW, int U>
+int launch_vec_mode(int mode, int grid, int threads, cudaStream_t st, uint4 *dstv, const uint4 *srcv, size_t nvec,
+                    int sb8, const Edges &e) {
+    switch (mode) {
+        case 1: copy_vec_kernel<SW, U, 1><<<grid, threads, 0, st>>>(dstv, srcv, nvec, sb8, e); break;
+        case 2: copy_vec_kernel<SW, U, 2><<<grid, threads, 0, st>>>(dstv, srcv, nvec, sb8, e); break;
+        default: copy_vec_kernel<SW, U, 0><<<grid, threads, 0, st>>>(dstv, srcv, nvec, sb8, e); break;
+    }
+    return check_launch();
+}
+
+template <int SW>
+int launch_vec_unroll(int unroll, int mode, int grid, int threads, cudaStream_t st, uint4 *dstv, const uint4 *srcv,
+                      size_t nvec, int sb8, const Edges &e) {
+    switch (unroll) {
+        case 1: return launch_vec_mode<SW, 1>(mode, grid, threads, st, dstv, srcv, nvec, sb8, e);
+        case 2: return launch_vec_mode<SW, 2>(mode, grid, threads, st, dstv, srcv, nvec, sb8, e);
+        case 8: return launch_vec_mode<SW, 8>(mode, grid, threads, st, dstv, srcv, nvec, sb8, e);
+        default: return launch_vec_mode<SW, 4>(mode, grid, threads, st, dstv, srcv, nvec, sb8, e);
+    }
+}
+
+int launch_vec(const Split &sp, int ctas, bool small, cudaStream_t st) {
+    const Tuning &tu = tuning();
+    int threads = small ? 128 : tu.copy_vec_threads;
+    int unroll = small ? 1 : tu.copy_vec_unroll;
+    if (!small) {
+        // mid sizes: shrink the per-warp tile until every SM gets work
+        const size_t want = (size_t)sm_count() * 2;
+        while (unroll > 1 && (sp.nvec / ((size_t)unroll * threads)) < want) unroll >>= 1;
+        while (threads > 128 && (sp.nvec / ((size_t)unroll * threads)) < want) threads >>= 1;
+    }
+    const size_t per_cta = (size_t)unroll * threads;
+    size_t need = (sp.nvec + per_cta - 1) / per_cta;
+    if (need == 0) need = 1;
+    size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * tu.copy_vec_ctas_sm * (512 / threads);
+    const int grid = (int)(need < cap ? need : cap);
+
+    const uintptr_t sa = reinterpret_cast<uintptr_t>(sp.src_body);
+    const int s = (int)(sa & 15);
+    const uint4 *srcv = reinterpret_cast<const uint4 *>(sa - s);
+    const int sb8 = (s & 3) * 8;
+    const int mode = tu.copy_cache_mode;
+    if (s == 0) return launch_vec_unroll<-1>(unroll, mode, grid, threads, st, sp.dstv, srcv, sp.nvec, 0, sp.e);
+    switch (s >> 2) {
+        case 0: return launch_vec_unroll<0>(unroll, mode, grid, threads, st, sp.dstv, srcv, sp.nvec, sb8, sp.e);
+        case 1: return launch_vec_unroll<1>(unroll, mode, grid, threads, st, sp.dstv, srcv, sp.nvec, sb8, sp.e);
+        case 2: return launch_vec_unroll<2>(unroll, mode, grid, threads, st, sp.dstv, srcv, sp.nvec, sb8, sp.e);
+        default: return launch_vec_unroll<3>(unroll, mode, grid, threads, st, sp.dstv, srcv, sp.nvec, sb8, sp.e);
+    }
+}
+
+template <int S, int L>
+int launch_tma_cfg(bool hint, int grid, size_t smem, cudaStream_t st, uint8_t *d, const uint8_t *s, size_t body,
+                   uint32_t chunk, const Edges &e) {
+    cudaError_t err;
+    if (hint) {
+        err = cudaFuncSetAttribute(copy_tma_kernel<S, L, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return (int)err;
+        copy_tma_kernel<S, L, true><<<grid, 32, smem, st>>>(d, s, body, chunk, e);
+    } else {
+        err = cudaFuncSetAttribute(copy_tma_kernel<S, L, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return (int)err;
+        copy_tma_kernel<S, L, false><<<grid, 32, smem, st>>>(d, s, body, chunk, e);
+    }
+    return check_launch();
+}
+
+int launch_tma(const Split &sp, int ctas, cudaStream_t st) {
+    const Tuning &tu = tuning();
+    uint32_t chunk = (uint32_t)tu.tma_chunk;
+    if (chunk < 1024 || chunk > 65536 || (chunk & 127)) return 1;
+    const int S = tu.tma_stages, L = tu.tma_lookahead;
+    const size_t smem = (size_t)S * chunk + 8 * S;
+    if (smem > 227 * 1024) return 1;
+    const size_t body = sp.nvec * 16;
+    const size_t nchunks = (body + chunk - 1) / chunk;
+    size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * tu.tma_ctas_sm;
+    int grid = (int)(nchunks < cap ? (nchunks ? nchunks : 1) : cap);
+    uint8_t *d = reinterpret_cast<uint8_t *>(sp.dstv);
+    const bool hint = tu.tma_cache_hint != 0;
+#define LCB_TMA_CFG(S_, L_) \
+    if (S == S_ && L == L_) return launch_tma_cfg<S_, L_>(hint, grid, smem, st, d, sp.src_body, body, chunk, sp.e)
+    LCB_TMA_CFG(2, 1);
+    LCB_TMA_CFG(3, 2);
+    LCB_TMA_CFG(4, 2);
+    LCB_TMA_CFG(4, 3);
+    LCB_TMA_CFG(6, 3);
+    LCB_TMA_CFG(6, 4);
+    LCB_TMA_CFG(8, 4);
+    LCB_TMA_CFG(8, 6);
+    LCB_TMA_CFG(12, 8);
+    LCB_TMA_CFG(16, 8);
+    LCB_TMA_CFG(16, 12);
+#undef LCB_TMA_CFG
+    return 1;
+}
+
+}  // namespace
+}  // namespace lcb
+
+extern "C" int lcb_copy_d2d_ex(void *dst, const void *src, size_t bytes, int path, int ctas, lcbStream stream) {
+    using namespace lcb;
+    if (bytes == 0) return 0;
+    if (dst == nullptr || src == nullptr || ctas < 0) return 1;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const Split sp = split_copy(dst, src, bytes);
+    const bool mutual = ((reinterpret_cast<uintptr_t>(dst) ^ reinterpret_cast<uintptr_t>(src)) & 15) == 0;
+    if (path == LCB_COPY_AUTO) {
+        const Tuning &tu = tuning();
+        if (bytes < 64 * 1024) path = LCB_COPY_SMALL;
+        else if (mutual && tu.auto_tma_min_bytes >= 0 && bytes >= (size_t)tu.auto_tma_min_bytes) path = LCB_COPY_TMA;
+        else path = LCB_COPY_VEC;
+    }
+    switch (path) {
+        case LCB_COPY_VEC: return launch_vec(sp, ctas, false, st);
+        case LCB_COPY_SMALL: return launch_vec(sp, ctas, true, st);
+        case LCB_COPY_TMA:
+            if (!mutual) return 1;
+            return launch_tma(sp, ctas, st);
+        default: return 1;
+    }
+}
+
+extern "C" int lcb_copy_d2d(void *dst, const void *src, size_t bytes, lcbStream stream) {
+    return lcb_copy_d2d_ex(dst, src, bytes, LCB_COPY_AUTO, 0, stream);
+}
+
+extern "C" int lcb_alltoall_push(void *const *peer_recv, const void *send, size_t chunk_bytes, int n_ranks, int rank,
+                                 lcbStream stream) {
+    using namespace lcb;
+    if (n_ranks < 1 || n_ranks > 16 || rank < 0 || rank >= n_ranks || peer_recv == nullptr || send == nullptr) return 1;
+    if (chunk_bytes == 0) return 0;
+    if ((chunk_bytes & 15) || (reinterpret_cast<uintptr_t>(send) & 15)) return 1;
+    PeerPtrs pp{};
+    for (int j = 0; j < n_ranks; ++j) {
+        if (peer_recv[j] == nullptr || (reinterpret_cast<uintptr_t>(peer_recv[j]) & 15)) return 1;
+        pp.recv[j] = static_cast<uint4 *>(peer_recv[j]);
+    }
+    const Tuning &tu = tuning();
+    const int threads = 512;
+    const size_t chunk_vec = chunk_bytes / 16;
+    const size_t per_cta = (size_t)4 * threads;
+    size_t per_peer = (chunk_vec + per_cta - 1) / per_cta;
+    size_t cap = ((size_t)sm_count() * tu.copy_vec_ctas_sm + n_ranks - 1) / n_ranks;
+    if (per_peer > cap) per_peer = cap;
+    if (per_peer == 0) per_peer = 1;
+    const int grid = (int)(per_peer * n_ranks);
+    alltoall_push_kernel<4, 0><<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        pp, static_cast<const uint4 *>(send), chunk_vec, n_ranks, rank);
+    return check_launch();
+}
+
+extern "C" int lcb_device_error_word(unsigned int *out) {
+    if (out == nullptr) return 1;
+    cudaError_t err = cudaDeviceSynchronize();
+    if (err != cudaSuccess) return (int)err;
+    unsigned int w = 0;
+    err = cudaMemcpyFromSymbol(&w, lcb::g_error_word, sizeof(w));
+    if (err != cudaSuccess) return (int)err;
+    if (w) {
+        unsigned int zero = 0;
+        err = cudaMemcpyToSymbol(lcb::g_error_word, &zero, sizeof(zero));
+        if (err != cudaSuccess) return (int)err;
+    }
+    *out = w;
+    return 0;
+}
+

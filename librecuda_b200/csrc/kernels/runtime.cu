@@ -1,0 +1,121 @@
+// Process-wide state of the kernel layer: tunables, cached device properties, the sticky device error
+// word, and the small timing helpers the benchmark uses on raw CUDA streams.
+#include <cstring>
+
+#include "common.cuh"
+#include "lcb200_kernels.h"
+
+namespace lcb {
+
+Tuning &tuning() {
+    static Tuning t = {
+        /*copy_vec_threads*/ 512,
+        /*copy_vec_unroll*/ 4,
+        /*copy_vec_ctas_sm*/ 4,
+        /*copy_cache_mode*/ 0,
+        /*tma_chunk*/ 16384,
+        /*tma_stages*/ 8,
+        /*tma_lookahead*/ 4,
+        /*tma_ctas_sm*/ 1,
+        /*tma_cache_hint*/ 0,
+        /*auto_tma_min_bytes*/ -1,
+        /*memset_path*/ 0,
+        /*memset_unroll*/ 8,
+        /*memset_threads*/ 512,
+        /*memset_ctas_sm*/ 4,
+    };
+    return t;
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+int check_launch() { return (int)cudaGetLastError(); }
+
+}  // namespace lcb
+
+extern "C" int lcb_tune(const char *name, int value) {
+    using lcb::tuning;
+    if (name == nullptr) return 1;
+#define LCB_KNOB(field)                  \
+    if (std::strcmp(name, #field) == 0) { \
+        tuning().field = value;          \
+        return 0;                        \
+    }
+    LCB_KNOB(copy_vec_threads)
+    LCB_KNOB(copy_vec_unroll)
+    LCB_KNOB(copy_vec_ctas_sm)
+    LCB_KNOB(copy_cache_mode)
+    LCB_KNOB(tma_chunk)
+    LCB_KNOB(tma_stages)
+    LCB_KNOB(tma_lookahead)
+    LCB_KNOB(tma_ctas_sm)
+    LCB_KNOB(tma_cache_hint)
+    LCB_KNOB(auto_tma_min_bytes)
+    LCB_KNOB(memset_path)
+    LCB_KNOB(memset_unroll)
+    LCB_KNOB(memset_threads)
+    LCB_KNOB(memset_ctas_sm)
+#undef LCB_KNOB
+    return 1;
+}
+
+extern "C" const char *lcb_version(void) { return "lcb200 0.1 sm_100a"; }
+
+// ---- event timers on a raw stream ---------------------------------------------------------------
+struct lcbTimer_ {
+    cudaEvent_t start, stop;
+};
+
+extern "C" int lcb_timer_create(void **timer_out) {
+    if (timer_out == nullptr) return 1;
+    lcbTimer_ *t = new lcbTimer_();
+    cudaError_t err = cudaEventCreate(&t->start);
+    if (err == cudaSuccess) err = cudaEventCreate(&t->stop);
+    if (err != cudaSuccess) {
+        delete t;
+        return (int)err;
+    }
+    *timer_out = t;
+    return 0;
+}
+
+extern "C" int lcb_timer_start(void *timer, lcbStream stream) {
+    if (timer == nullptr) return 1;
+    return (int)cudaEventRecord(static_cast<lcbTimer_ *>(timer)->start, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int lcb_timer_stop(void *timer, lcbStream stream) {
+    if (timer == nullptr) return 1;
+    return (int)cudaEventRecord(static_cast<lcbTimer_ *>(timer)->stop, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int lcb_timer_elapsed_ms(void *timer, float *ms_out) {
+    if (timer == nullptr || ms_out == nullptr) return 1;
+    lcbTimer_ *t = static_cast<lcbTimer_ *>(timer);
+    cudaError_t err = cudaEventSynchronize(t->stop);
+    if (err != cudaSuccess) return (int)err;
+    return (int)cudaEventElapsedTime(ms_out, t->start, t->stop);
+}
+
+extern "C" int lcb_timer_destroy(void *timer) {
+    if (timer == nullptr) return 1;
+    lcbTimer_ *t = static_cast<lcbTimer_ *>(timer);
+    cudaEventDestroy(t->start);
+    cudaEventDestroy(t->stop);
+    delete t;
+    return 0;
+}
+
+extern "C" int lcb_stream_synchronize(lcbStream stream) {
+    return (int)cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+}

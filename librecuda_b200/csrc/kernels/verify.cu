@@ -1,0 +1,159 @@
+// Device-side verification helpers: byte comparison of two buffers and an order-independent checksum.
+// They let full-size parity checks (multi-GiB buffers) run at HBM speed instead of over PCIe.
+// No counterpart in the reference, whose tests compare on the host after a DtoH copy
+// (tests/dma_chronological_consistency/main.cpp:73-85).
+#include "common.cuh"
+#include "lcb200_kernels.h"
+
+namespace lcb {
+
+// 8 bytes starting `sh8/8` bytes into the aligned word stream p[i], p[i+1] (second word only touched
+// when the shift is non-zero, so no read past the word holding the last valid byte).
+__device__ __forceinline__ uint64_t load_shifted(const uint64_t *p, size_t i, int sh8) {
+    uint64_t lo = p[i];
+    if (sh8 == 0) return lo;
+    uint64_t hi = p[i + 1];
+    return (lo >> sh8) | (hi << (64 - sh8));
+}
+
+__global__ void compare_init_kernel(unsigned long long *result) {
+    result[0] = 0ull;
+    result[1] = ~0ull;
+}
+
+// a_al / b_al: pointers rounded down to 8 bytes, sa8 / sb8: 8 * (pointer & 7).
+__global__ void __launch_bounds__(512) compare_kernel(const uint64_t *__restrict__ a_al, int sa8,
+                                                      const uint64_t *__restrict__ b_al, int sb8,
+                                                      const uint8_t *a, const uint8_t *b, size_t nwords, size_t bytes,
+                                                      unsigned long long *result) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    unsigned long long bad = 0, first = ~0ull;
+    for (size_t i = tid; i < nwords; i += stride) {
+        const uint64_t x = load_shifted(a_al, i, sa8) ^ load_shifted(b_al, i, sb8);
+        if (x) {
+            // count differing bytes, remember the first one
+            int nb = 0, fb = -1;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if ((x >> (8 * k)) & 0xff) {
+                    ++nb;
+                    if (fb < 0) fb = k;
+                }
+            }
+            bad += nb;
+            const unsigned long long pos = (unsigned long long)i * 8 + fb;
+            if (pos < first) first = pos;
+        }
+    }
+    if (tid == 0) {  // trailing bytes, one by one
+        for (size_t i = nwords * 8; i < bytes; ++i) {
+            if (a[i] != b[i]) {
+                ++bad;
+                if (i < first) first = i;
+            }
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        bad += __shfl_down_sync(0xffffffffu, bad, o);
+        const unsigned long long f2 = __shfl_down_sync(0xffffffffu, first, o);
+        if (f2 < first) first = f2;
+    }
+    if ((threadIdx.x & 31) == 0 && bad) {
+        atomicAdd(result, bad);
+        atomicMin(result + 1, first);
+    }
+}
+
+constexpr int kChecksumMaxCtas = 2048;
+
+// scratch[0] = ticket counter (must be zero at launch; left zero again at exit), scratch[1 + b] = partial of CTA b.
+__global__ void __launch_bounds__(512) checksum_kernel(const uint64_t *__restrict__ src, size_t nwords,
+                                                       const uint8_t *tail, int tail_bytes,
+                                                       unsigned long long *scratch, unsigned long long *out) {
+    __shared__ unsigned long long warp_sums[16];
+    __shared__ bool is_last;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    unsigned long long acc = 0;
+    for (size_t i = tid; i < nwords; i += stride) acc += mix64(src[i] + i * kGolden);
+    if (tid == 0 && tail_bytes) {
+        uint64_t w = 0;
+        for (int b = 0; b < tail_bytes; ++b) w |= (uint64_t)tail[b] << (8 * b);
+        acc += mix64(w + nwords * kGolden);
+    }
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long s = 0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += warp_sums[w];
+        scratch[1 + blockIdx.x] = s;
+        __threadfence();
+        const unsigned long long ticket = atomicAdd(scratch, 1ull);
+        is_last = (ticket == (unsigned long long)gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    unsigned long long s = 0;
+    for (int b = threadIdx.x; b < (int)gridDim.x; b += blockDim.x) s += ((volatile unsigned long long *)scratch)[1 + b];
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long total = 0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) total += warp_sums[w];
+        out[0] = total;
+        scratch[0] = 0ull;  // ready for the next launch
+    }
+}
+
+}  // namespace lcb
+
+extern "C" int lcb_compare_bytes(const void *a, const void *b, size_t bytes, uint64_t *result, lcbStream stream) {
+    using namespace lcb;
+    if (result == nullptr) return 1;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned long long *res = reinterpret_cast<unsigned long long *>(result);
+    compare_init_kernel<<<1, 1, 0, st>>>(res);
+    int rc = check_launch();
+    if (rc || bytes == 0) return rc;
+    if (a == nullptr || b == nullptr) return 1;
+    const uintptr_t pa = reinterpret_cast<uintptr_t>(a), pb = reinterpret_cast<uintptr_t>(b);
+    const size_t nwords = bytes / 8;
+    const int threads = 512;
+    size_t need = (nwords + threads - 1) / threads;
+    if (need == 0) need = 1;
+    const size_t cap = (size_t)sm_count() * 4;
+    const int grid = (int)(need < cap ? need : cap);
+    compare_kernel<<<grid, threads, 0, st>>>(reinterpret_cast<const uint64_t *>(pa & ~(uintptr_t)7), (int)(pa & 7) * 8,
+                                             reinterpret_cast<const uint64_t *>(pb & ~(uintptr_t)7), (int)(pb & 7) * 8,
+                                             static_cast<const uint8_t *>(a), static_cast<const uint8_t *>(b), nwords,
+                                             bytes, res);
+    return check_launch();
+}
+
+extern "C" size_t lcb_checksum_scratch_bytes(void) { return sizeof(uint64_t) * (1 + lcb::kChecksumMaxCtas); }
+
+extern "C" int lcb_checksum64(const void *src, size_t bytes, uint64_t *scratch, uint64_t *out, lcbStream stream) {
+    using namespace lcb;
+    if (src == nullptr || scratch == nullptr || out == nullptr) return 1;
+    if (reinterpret_cast<uintptr_t>(src) & 7) return 1;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t err = cudaMemsetAsync(scratch, 0, sizeof(uint64_t), st);  // ticket counter starts at zero
+    if (err != cudaSuccess) return (int)err;
+    const size_t nwords = bytes / 8;
+    const int threads = 512;
+    size_t need = (nwords + threads - 1) / threads;
+    if (need == 0) need = 1;
+    size_t cap = (size_t)sm_count() * 4;
+    if (cap > (size_t)kChecksumMaxCtas) cap = kChecksumMaxCtas;
+    const int grid = (int)(need < cap ? need : cap);
+    checksum_kernel<<<grid, threads, 0, st>>>(static_cast<const uint64_t *>(src), nwords,
+                                              static_cast<const uint8_t *>(src) + nwords * 8, (int)(bytes - nwords * 8),
+                                              reinterpret_cast<unsigned long long *>(scratch),
+                                              reinterpret_cast<unsigned long long *>(out));
+    return check_launch();
+}

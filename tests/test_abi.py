@@ -1,0 +1,116 @@
+"""The C-ABI boundary, without a GPU: the shared library loads, exports every symbol the public headers
+declare (functions and the status data symbols), and the host-only logic behaves like the reference's."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import oracle
+from librecuda_b200 import _native as N
+from librecuda_b200 import api
+
+INCLUDE = Path(__file__).resolve().parent.parent / "include"
+
+
+def _declared(header: str, prefix: str):
+    text = (INCLUDE / header).read_text()
+    text = re.sub(r"//.*", "", text)
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(" + prefix + r"\w+)\s*\(", text)))
+
+
+def test_every_lcb_symbol_is_exported_and_bound():
+    names = _declared("lcb200_kernels.h", "lcb_")
+    assert len(names) >= 20
+    for name in names:
+        assert hasattr(N.lib, name), f"{name} declared in lcb200_kernels.h but not exported"
+        assert name in N.LCB_FUNCTIONS, f"{name} has no ctypes prototype"
+
+
+def test_every_librecu_symbol_is_exported_and_bound():
+    names = _declared("librecuda.h", "libreCu")
+    assert len(names) >= 30 + 25
+    for name in names:
+        assert hasattr(N.lib, name), f"{name} declared in librecuda.h but not exported"
+        assert name in N.LIBRECU_FUNCTIONS, f"{name} has no ctypes prototype"
+
+
+def test_reference_surface_is_complete():
+    # the 30 entry points of the reference header (driverapi/include/librecuda.h:37-114)
+    ref30 = """libreCuInit libreCuDeviceGetCount libreCuDeviceGet libreCuGetErrorString libreCuCtxCreate_v2
+    libreCuCtxDestroy libreCuCtxSetCurrent libreCuCtxGetCurrent libreCuMemAlloc libreCuMemCpy libreCuMemFree
+    libreCuStreamCreate libreCuStreamDestroy libreCuDeviceGetName libreCuDeviceGetAttribute libreCuFuncSetAttribute
+    libreCuModuleLoadData libreCuModuleGetFunctionCount libreCuModuleEnumerateFunctions libreCuFuncGetName
+    libreCuModuleGetFunction libreCuLaunchKernel libreCuEventCreate libreCuEventRecord libreCuEventSynchronize
+    libreCuEventElapsedTime libreCuEventDestroy libreCuStreamCommence libreCuStreamAwait libreCuModuleUnload""".split()
+    assert len(ref30) == 30
+    for name in ref30:
+        assert hasattr(N.lib, name)
+
+
+def test_status_values_are_data_symbols():
+    for name, value in N.STATUS_VARIABLES.items():
+        assert C.c_int.in_dll(N.lib, name).value == value
+        assert api.error_string(value) == name
+    assert api.error_string(12345) is None  # unknown code: null name, success status
+
+
+@pytest.mark.skipif(oracle.ref is None, reason="oracle/_ref not built (no reference checkout)")
+def test_status_names_match_reference_table():
+    for value in list(N.STATUS_VARIABLES.values()) + [7, 12345]:
+        want = oracle.ref.ref_status_name(value)
+        got = api.error_string(value)
+        assert (want.decode() if want else None) == got
+
+
+def test_version_string():
+    assert N.lib.lcb_version().startswith(b"lcb200")
+
+
+def test_calls_before_init_or_without_context_fail_like_the_reference(gpu_count):
+    n = C.c_int()
+    if gpu_count == 0:
+        # no driver here: init must fail loudly, never fall back
+        assert N.lib.libreCuInit(0) == api.ERROR_COMPAT_NOT_SUPPORTED_ON_DEVICE
+        assert N.lib.libreCuDeviceGetCount(C.byref(n)) == api.ERROR_NOT_INITIALIZED
+        p = C.c_void_p()
+        assert N.lib.libreCuMemAlloc(C.byref(p), 4096, False) == api.ERROR_INVALID_CONTEXT
+        s = C.c_void_p()
+        assert N.lib.libreCuStreamCreate(C.byref(s), 0) == api.ERROR_INVALID_CONTEXT
+    assert N.lib.libreCuDeviceGetCount(None) == api.ERROR_INVALID_VALUE
+    assert N.lib.libreCuMemCpy(None, None, 4, None, False) == api.ERROR_INVALID_VALUE
+    assert N.lib.libreCuMemFree(None) == api.ERROR_INVALID_VALUE
+    assert N.lib.libreCuCtxSetCurrent(None) == api.ERROR_INVALID_CONTEXT
+    assert N.lib.libreCuCtxDestroy(None) == api.ERROR_INVALID_CONTEXT
+    assert N.lib.libreCuEventSynchronize(None) == api.ERROR_INVALID_VALUE
+
+
+def test_kernel_layer_rejects_bad_arguments_without_touching_a_gpu():
+    assert N.lib.lcb_copy_d2d(None, None, 0, None) == 0          # empty copy is a no-op
+    assert N.lib.lcb_copy_d2d(None, 16, 16, None) == 1
+    assert N.lib.lcb_copy_d2d_ex(16, 32, 16, 99, 0, None) == 1   # unknown path
+    assert N.lib.lcb_copy_d2d_ex(16, 33, 64, 2, 0, None) == 1    # bulk path needs congruent pointers
+    assert N.lib.lcb_memset_ex(16, 0, 3, 4, 0, 0, None) == 1     # element size 3
+    assert N.lib.lcb_memset_d32(18, 0, 4, None) == 1             # misaligned for 4-byte elements
+    assert N.lib.lcb_memset_d8(None, 0, 0, None) == 0
+    assert N.lib.lcb_index_fill_f32(6, 4, None) == 1
+    assert N.lib.lcb_tune(b"no_such_knob", 1) == 1
+    assert N.lib.lcb_checksum_scratch_bytes() >= 8 * 1185
+    peers = (C.c_void_p * 2)(4096, 8192)
+    assert N.lib.lcb_alltoall_push(peers, 4096, 24, 2, 0, None) == 1   # chunk not a multiple of 16
+    assert N.lib.lcb_alltoall_push(peers, 4096, 32, 2, 5, None) == 1   # rank out of range
+
+
+@pytest.mark.parametrize("total,parts,align", [(8 << 30, 8, 0), (8 << 30, 4, 2 << 20), (10 * (1 << 20) + 5, 4, 2 << 20),
+                                               (1 << 20, 8, 0), (0, 3, 4096), (4097, 2, 4096), (100, 7, 16), (5, 1, 16)])
+def test_partition_plan_matches_oracle(total, parts, align):
+    assert api.partition_plan(total, parts, align) == oracle.partition(total, parts, align or (2 << 20))
+
+
+def test_partition_plan_rejects_bad_arguments():
+    out = (C.c_size_t * 4)()
+    assert N.lib.libreCuPartitionPlan(100, 0, 16, out) == api.ERROR_INVALID_VALUE
+    assert N.lib.libreCuPartitionPlan(100, 2, 24, out) == api.ERROR_INVALID_VALUE
+    assert N.lib.libreCuPartitionPlan(100, 2, 16, None) == api.ERROR_INVALID_VALUE
