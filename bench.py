@@ -1,0 +1,468 @@
+#!/usr/bin/env python
+"""Benchmark of the data-movement hot path: device-to-device copy GB/s (read + write bytes counted).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one DtoD copy of a 1 GiB buffer (inputs larger than L2, so no flush is needed between steps).
+`value` times the copy kernel through the C-ABI (lcb_copy_d2d) with the source already in HBM; `e2e` times
+the same copy through the public libreCu* API from pinned HOST buffers (HtoD -> DtoD -> DtoH inside the
+timed region).  With N > 1 (one process per GPU under torchrun) every rank copies its own 1 GiB shard --
+weak scaling, no data-path collective -- and the NVLink paths (peer push, all-to-all, broadcast) are
+measured as well and reported under "nvlink".  Rank 0 prints one JSON line.
+
+`--impl reference` times the reference's CPU statement of the path -- multithreaded memcpy on the host
+cores (oracle/lcb_oracle.c) -- on the same workload and metric.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import shutil
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+GiB = 1 << 30
+MiB = 1 << 20
+WORKLOAD_BYTES = GiB
+METRIC = "dtod_copy_GBps"
+UNIT = "GB/s"
+NVLINK_NOMINAL = 900.0   # GB/s per direction per GPU
+NVLINK_MEASURED = 770.0  # GB/s, peer copy measured on this pool
+
+
+def measured_hbm_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+# ---------------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        exe = shutil.which("nvidia-smi")
+        if exe is None:
+            return
+        fd, self.path = tempfile.mkstemp(suffix=".csv")
+        os.close(fd)
+        self.proc = subprocess.Popen(
+            [exe, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.gpu)],
+            stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        time.sleep(0.3)
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in Path(self.path).read_text().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, parts[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if not sm:
+            return None
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------
+# reference arm: the CPU statement of the path on the host cores
+# ---------------------------------------------------------------------------------------------------
+def cpu_memcpy_gbps(nbytes: int, threads: int, reps: int):
+    import numpy as np
+
+    import oracle  # CPU baseline leg: the one place the benchmark executes the oracle
+
+    src = oracle.random_bytes(nbytes, seed=1)
+    dst = np.zeros(nbytes, np.uint8)
+    best = oracle.mt_seconds(dst, src, op=0, value=0, threads=threads, reps=reps)
+    return 2.0 * nbytes / best / 1e9, best
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    import numpy as np
+
+    import oracle
+
+    threads = host_threads()
+    n = WORKLOAD_BYTES
+    src = oracle.random_bytes(n, seed=1)
+    dst = np.zeros(n, np.uint8)
+    for _ in range(max(args.warmup, 1)):
+        oracle.mt_seconds(dst, src, 0, 0, threads, 1)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.mt_seconds(dst, src, 0, 0, threads, 1)
+    dt = time.perf_counter() - t0
+    ms = dt / args.steps * 1e3
+    value = 2.0 * n / (dt / args.steps) / 1e9
+    assert np.array_equal(dst[:4096], src[:4096])
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": "dtod_copy_1GiB_aligned", "bytes": n, "seed": 1,
+                   "note": "reference's CPU statement of the path: multithreaded memcpy of the same seeded bytes"},
+        "cpu_baseline": {"value": round(value, 2), "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{args.steps} x memcpy of 1 GiB split over {threads} threads"},
+        "e2e": {"value": round(value, 2), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ---------------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------------
+def timed_loop(api, stream, fn, steps):
+    """fn() enqueues one step on stream.native; returns average ms per step (CUDA events on that stream)."""
+    t = api.Timer()
+    t.start(stream.native)
+    for _ in range(steps):
+        fn()
+    t.stop(stream.native)
+    ms = t.elapsed_ms() / steps
+    t.destroy()
+    return ms
+
+
+def run_ours(args):
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    multi = world > 1
+    dist = None
+    torch = None
+    if multi:
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from librecuda_b200 import api
+
+    lib = api.lib
+    ctx = api.Context(local_rank, api.CU_CTX_SCHED_YIELD)
+    stream = api.Stream()
+    native = stream.native
+    n = WORKLOAD_BYTES
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    def barrier():
+        if multi:
+            dist.barrier()
+            torch.cuda.synchronize()
+        api.lcb_check(lib.lcb_stream_synchronize(native), "sync")
+
+    def max_over_ranks(ms: float) -> float:
+        if not multi:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    src, dst = api.DeviceBuffer(n), api.DeviceBuffer(n)
+    res = api.DeviceBuffer(16)
+    api.lcb_check(lib.lcb_fill_splitmix64(src.ptr, n, 1 + rank, native), "fill")
+    stream.memset_d8(dst, 0, n)
+    stream.run()
+
+    def copy_step():
+        api.lcb_check(lib.lcb_copy_d2d(dst.ptr, src.ptr, n, native), "lcb_copy_d2d")
+
+    for _ in range(warmup):
+        copy_step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    ms_local = timed_loop(api, stream, copy_step, steps)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = max_over_ranks(ms_local)
+    value = world * 2.0 * n / (ms * 1e-3) / 1e9
+    launches = steps
+
+    # bit-exactness of what was just timed (device-side compare, outside the timed region)
+    api.lcb_check(lib.lcb_compare_bytes(dst.ptr, src.ptr, n, res.ptr, native), "compare")
+    import numpy as np
+
+    r = np.zeros(2, np.uint64)
+    stream.memcpy(r, res, 16)
+    stream.run()
+    verified = int(r[0]) == 0 and api.device_error_word() == 0
+
+    peak, peak_kind = measured_hbm_peak()
+    achieved = 2.0 * n / (ms_local * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "lcb_copy_d2d (1 GiB, 16-byte aligned)", "achieved": round(achieved, 1),
+                "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                "frac_of_nominal_8000": round(achieved / 8000.0, 4), "traffic": None}
+
+    # other single-GPU paths of the metric: memset D32 and index fill over 1 GiB (bytes written counted once)
+    also = {}
+    words = n // 4
+    for name, fn in (("memset_d32_1GiB", lambda: api.lcb_check(lib.lcb_memset_d32(dst.ptr, 0x40490FDB, words, native), "memset")),
+                     ("memset_d8_1GiB", lambda: api.lcb_check(lib.lcb_memset_d8(dst.ptr, 0xA5, n, native), "memset")),
+                     ("index_fill_f32_1GiB", lambda: api.lcb_check(lib.lcb_index_fill_f32(dst.ptr, words, native), "index_fill"))):
+        for _ in range(3):
+            fn()
+        barrier()
+        t_ms = timed_loop(api, stream, fn, steps)
+        gbps = n / (t_ms * 1e-3) / 1e9
+        also[name] = {"GBps": round(gbps, 1), "ms": round(t_ms, 4), "frac_of_measured_hbm": round(gbps / peak, 4),
+                      "frac_of_nominal_8000": round(gbps / 8000.0, 4)}
+
+    # end to end through the public API with HOST buffers: HtoD -> DtoD -> DtoH inside the timed region
+    e2e = run_e2e(api, ctx, n, max(2, min(steps, 10)), max_over_ranks, barrier, world)
+
+    nvlink = run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_ranks) if multi else None
+
+    cpu = None
+    if rank == 0 and not multi:
+        threads = host_threads()
+        v, best = cpu_memcpy_gbps(n, threads, reps=8)
+        cpu = {"value": round(v, 2), "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"best of 8 x memcpy of the same 1 GiB seeded buffer split over {threads} threads"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u8", "data": "synthetic",
+            "config": {"workload": "dtod_copy_1GiB_aligned", "bytes_per_gpu": n, "seed": 1,
+                       "algorithmic_bytes_per_step_per_gpu": 2 * n,
+                       "l2": "inputs larger than L2 (1 GiB source + 1 GiB destination per step), no flush",
+                       "parallelism": f"{world} independent shards, no data-path collective"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "verified_bit_exact": verified, "also": also,
+        }
+        if nvlink is not None:
+            line["nvlink"] = nvlink
+        print(json.dumps(line))
+    for b in (src, dst, res):
+        b.free()
+    stream.destroy()
+    if multi:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0 if verified else 1
+
+
+def run_e2e(api, ctx, n, steps, max_over_ranks, barrier, world):
+    """The call sequence a user of the API makes (reference tests/memcopy/main.cpp:47-57) on pinned host
+    buffers, timed with the API's own events."""
+    import numpy as np
+
+    st = api.Stream()
+    hin, hout = api.PinnedBuffer(n), api.PinnedBuffer(n)
+    hin.array[:] = np.arange(n, dtype=np.uint8) if n <= (1 << 20) else np.resize(np.arange(251, dtype=np.uint8), n)
+    a, b = api.DeviceBuffer(n), api.DeviceBuffer(n)
+    start, end = api.Event(), api.Event()
+
+    def record_step():
+        st.memcpy(a, hin.array, n)
+        st.memcpy(b, a, n)
+        st.memcpy(hout.array, b, n)
+
+    record_step()
+    record_step()
+    st.run()
+    barrier()
+    start.record(st)
+    for _ in range(steps):
+        record_step()
+    end.record(st)
+    st.run()
+    ms = api.elapsed_ms(start, end) / steps
+    ok = bool(np.array_equal(hout.array[:: 4099], hin.array[:: 4099]) and np.array_equal(hout.array[-4096:], hin.array[-4096:]))
+    ms = max_over_ranks(ms)
+    for e in (start, end):
+        e.destroy()
+    for x in (a, b):
+        x.free()
+    hin.free()
+    hout.free()
+    st.destroy()
+    return {"value": round(world * 2.0 * n / (ms * 1e-3) / 1e9, 2), "unit": UNIT, "h2d_bytes_per_step": n,
+            "d2h_bytes_per_step": n, "ms_per_step": round(ms, 3), "steps": steps, "verified": ok,
+            "path": "libreCuMemCpy HtoD -> DtoD -> DtoH on pinned host buffers, timed with libreCuEvent*"}
+
+
+def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_ranks):
+    """NVLink paths at world size G: peer push (rank r -> r+1), all-to-all (own fused push kernel and NCCL),
+    broadcast from rank 0 (NCCL).  GB/s per GPU per direction; fractions of 900 (nominal) and 770 (measured)."""
+    import numpy as np
+
+    lib = api.lib
+    native = stream.native
+    G = world
+    chunk = GiB if G <= 4 else GiB // 2  # all-to-all chunk per pair; (G-1) * chunk leaves every GPU
+    shard = GiB
+    send = api.DeviceBuffer(G * chunk)
+    recv = api.DeviceBuffer(G * chunk)
+    api.lcb_check(lib.lcb_fill_splitmix64(send.ptr, G * chunk, 100 + rank, native), "fill")
+    stream.memset_d8(recv, 0, G * chunk)
+    stream.run()
+    handle = C.create_string_buffer(72)
+    api.check(lib.libreCuIpcGetMemHandle(handle, recv.ptr), "libreCuIpcGetMemHandle")
+    handles = [None] * G
+    dist.all_gather_object(handles, handle.raw)
+    peers = []
+    for r in range(G):
+        if r == rank:
+            peers.append(recv.ptr)
+        else:
+            p = C.c_void_p()
+            api.check(lib.libreCuIpcOpenMemHandle(C.byref(p), handles[r]), "libreCuIpcOpenMemHandle")
+            peers.append(p.value)
+    peer_arr = (C.c_void_p * G)(*peers)
+    out = {"world": G, "nominal_GBps": NVLINK_NOMINAL, "measured_peer_copy_GBps": NVLINK_MEASURED}
+
+    def report(name, bytes_per_gpu, ms):
+        gbps = bytes_per_gpu / (ms * 1e-3) / 1e9
+        out[name] = {"GBps_per_gpu_per_direction": round(gbps, 1), "ms": round(ms, 4),
+                     "frac_of_nominal_900": round(gbps / NVLINK_NOMINAL, 4),
+                     "frac_of_measured_770": round(gbps / NVLINK_MEASURED, 4)}
+
+    # 1. partitioned peer push: every rank stores its shard into the next rank's buffer (all ports busy)
+    nxt = peers[(rank + 1) % G]
+
+    def push():
+        api.lcb_check(lib.lcb_copy_d2d(nxt, send.ptr, shard, native), "peer push")
+
+    for _ in range(3):
+        push()
+    barrier()
+    ms = max_over_ranks(timed_loop(api, stream, push, steps))
+    barrier()
+    report("p2p_shift_push_1GiB", shard, ms)
+
+    # 2. all-to-all, own kernel: one launch stores every chunk into its peer slot
+    def a2a():
+        api.lcb_check(lib.lcb_alltoall_push(peer_arr, send.ptr, chunk, G, rank, native), "alltoall push")
+
+    for _ in range(3):
+        a2a()
+    barrier()
+    ms = max_over_ranks(timed_loop(api, stream, a2a, steps))
+    barrier()
+    report("alltoall_own_push", (G - 1) * chunk, ms)
+    # verify: slot r of my recv buffer must be chunk `rank` of rank r's send buffer
+    ok = True
+    resb = api.DeviceBuffer(16)
+    for r in range(G):
+        # regenerate rank r's send buffer up to chunk `rank` (the generator is keyed by position)
+        full = api.DeviceBuffer((rank + 1) * chunk)
+        api.lcb_check(lib.lcb_fill_splitmix64(full.ptr, (rank + 1) * chunk, 100 + r, native), "fill")
+        api.lcb_check(lib.lcb_compare_bytes(recv.ptr + r * chunk, full.ptr + rank * chunk, chunk, resb.ptr, native), "cmp")
+        got = np.zeros(2, np.uint64)
+        stream.memcpy(got, resb, 16)
+        stream.run()
+        ok = ok and int(got[0]) == 0
+        full.free()
+    out["alltoall_own_push"]["verified"] = ok
+
+    # 3. all-to-all and broadcast through NCCL (torch.distributed): the named library path
+    ts = torch.empty(G * chunk, dtype=torch.uint8, device="cuda")
+    tr = torch.empty(G * chunk, dtype=torch.uint8, device="cuda")
+    ts.random_(0, 256)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        dist.all_to_all_single(tr, ts)
+    barrier()
+    ev0.record()
+    for _ in range(steps):
+        dist.all_to_all_single(tr, ts)
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = max_over_ranks(ev0.elapsed_time(ev1) / steps)
+    report("alltoall_nccl", (G - 1) * chunk, ms)
+    del ts, tr
+    bsz = 4 * GiB
+    tb = torch.empty(bsz, dtype=torch.uint8, device="cuda")
+    if rank == 0:
+        tb.random_(0, 256)
+    for _ in range(2):
+        dist.broadcast(tb, 0)
+    barrier()
+    ev0.record()
+    for _ in range(max(2, steps // 2)):
+        dist.broadcast(tb, 0)
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = max_over_ranks(ev0.elapsed_time(ev1) / max(2, steps // 2))
+    report("broadcast_nccl_4GiB", bsz, ms)
+    del tb
+    barrier()
+    for r in range(G):
+        if r != rank:
+            api.check(lib.libreCuIpcCloseMemHandle(peers[r]), "libreCuIpcCloseMemHandle")
+    barrier()
+    for b in (send, recv, resb):
+        b.free()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,211 @@
+"""Parity of the device-to-device copy kernels (called through the C-ABI) with the oracle: bit-exact
+against host memcpy on the same seeded bytes, guard bands intact, for every path, alignment class and size
+class, plus the golden vectors generated from the reference."""
+import hashlib
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import oracle
+from librecuda_b200 import api
+from gpu_util import GUARD, GUARD_BYTE, device_checksum, device_compare, to_device, to_host
+
+pytestmark = pytest.mark.gpu
+MiB = 1 << 20
+AUTO, VEC, TMA, SMALL = 0, 1, 2, 3
+GOLDEN = json.loads((Path(__file__).parent / "golden" / "ref_d2d_golden.json").read_text())
+
+
+def _copy(stream, dst, src, n, path=AUTO, ctas=0):
+    api.lcb_check(api.lib.lcb_copy_d2d_ex(dst, src, n, path, ctas, stream.native), "lcb_copy_d2d_ex")
+
+
+def _run_cases(stream, cases, path):
+    """cases: list of (size, src_off, dst_off).  All copies go into one arena, one read-back, host check."""
+    slot = lambda n: (n + 2 * GUARD + 64 + 255) // 256 * 256
+    total = sum(slot(n) for n, _, _ in cases)
+    src_h = oracle.random_bytes(total, seed=1)
+    dst_h = np.full(total, GUARD_BYTE, np.uint8)
+    src_d, dst_d = api.DeviceBuffer(total), api.DeviceBuffer(total)
+    to_device(stream, src_d, src_h)
+    to_device(stream, dst_d, dst_h)
+    pos = 0
+    placed = []
+    for n, so, do in cases:
+        s, d = pos + GUARD + so, pos + GUARD + do
+        _copy(stream, dst_d.ptr + d, src_d.ptr + s, n, path)
+        placed.append((n, s, d))
+        pos += slot(n)
+    got = to_host(stream, dst_d, total)
+    want = dst_h.copy()
+    for n, s, d in placed:
+        oracle.lib.orc_memcpy(want[d:].ctypes.data, src_h[s:].ctypes.data, n)
+    bad = np.flatnonzero(got != want)
+    src_d.free()
+    dst_d.free()
+    if bad.size:
+        i = int(bad[0])
+        which = [(n, s, d) for n, s, d in placed if d - GUARD <= i < d + n + GUARD]
+        raise AssertionError(f"first mismatch at arena byte {i} (case size/src/dst {which}), {bad.size} bytes differ")
+    assert api.device_error_word() == 0
+
+
+SMALL_SIZES = sorted(set(range(0, 100)) | {127, 128, 129, 255, 256, 257, 511, 512, 513, 1023, 1024, 1025, 4095, 4096,
+                                           4097, 8191, 16384 + 5, 65535, 65536, 65537})
+OFFSETS = [0, 1, 2, 3, 4, 5, 7, 8, 9, 12, 13, 15, 16, 17, 31, 64]
+
+
+@pytest.mark.parametrize("path", [AUTO, VEC, SMALL])
+def test_small_sizes_all_alignment_classes(stream, path):
+    # every (src mod 16, dst mod 16) relation incl. all 15 realign shifts, every head/tail length
+    cases = [(n, so, do) for n in SMALL_SIZES for so in OFFSETS for do in (0, 1, 3, 7, 8, 15)]
+    _run_cases(stream, cases, path)
+
+
+def test_all_sixteen_by_sixteen_phase_pairs(stream):
+    cases = [(1000 + 3 * so + do, so, do) for so in range(16) for do in range(16)]
+    _run_cases(stream, cases, VEC)
+    _run_cases(stream, [(70000 + so, so, do) for so in range(16) for do in range(16)], AUTO)
+
+
+@pytest.mark.parametrize("path", [AUTO, VEC, TMA])
+def test_mid_and_large_sizes(stream, path):
+    sizes = [MiB - 1, MiB, MiB + 131, 2 * MiB + 5, 3 * MiB + 4099, 16 * MiB + 4100, 64 * MiB + 17]
+    offs = [(0, 0), (64, 64), (16, 48)] if path == TMA else [(0, 0), (1, 0), (0, 3), (7, 7), (64, 1), (3, 64), (5, 9)]
+    _run_cases(stream, [(n, so, do) for n in sizes for so, do in offs], path)
+
+
+def test_bulk_path_edges_and_small_bodies(stream):
+    # congruent but not 16-byte aligned pointers: head and tail bytes ride along with the bulk ring
+    cases = [(n, o, o + 16 * k) for n in (0, 1, 15, 16, 17, 31, 33, 1000, 16384, 16385, 3 * 16384 + 7, 200001)
+             for o in (0, 1, 5, 15) for k in (0, 2)]
+    _run_cases(stream, cases, TMA)
+
+
+def test_bulk_path_rejects_mutually_misaligned(stream):
+    a = api.DeviceBuffer(4096)
+    assert api.lib.lcb_copy_d2d_ex(a.ptr + 1, a.ptr + 2048, 64, TMA, 0, stream.native) == 1
+    a.free()
+
+
+@pytest.mark.parametrize("knobs", [dict(tma_stages=4, tma_lookahead=2, tma_chunk=8192),
+                                   dict(tma_stages=8, tma_lookahead=6, tma_chunk=16384, tma_cache_hint=1),
+                                   dict(tma_stages=16, tma_lookahead=12, tma_chunk=8192, tma_ctas_sm=1),
+                                   dict(tma_stages=3, tma_lookahead=2, tma_chunk=65536),
+                                   dict(tma_stages=6, tma_lookahead=3, tma_chunk=32768, tma_ctas_sm=1)])
+def test_bulk_ring_configurations(stream, knobs):
+    try:
+        api.tune(**knobs)
+        _run_cases(stream, [(n, o, o) for n in (5 * MiB + 48, 333333, 65536 * 7) for o in (0, 16)], TMA)
+    finally:
+        api.tune(tma_stages=8, tma_lookahead=4, tma_chunk=16384, tma_ctas_sm=1, tma_cache_hint=0)
+
+
+@pytest.mark.parametrize("knobs", [dict(copy_vec_unroll=1), dict(copy_vec_unroll=2), dict(copy_vec_unroll=8),
+                                   dict(copy_vec_threads=256, copy_cache_mode=1), dict(copy_cache_mode=2),
+                                   dict(copy_vec_threads=128, copy_vec_unroll=8, copy_vec_ctas_sm=2)])
+def test_vector_kernel_configurations(stream, knobs):
+    try:
+        api.tune(**knobs)
+        _run_cases(stream, [(n, so, do) for n in (9 * MiB + 77, 123457) for so, do in [(0, 0), (3, 0), (0, 9), (64, 6)]], VEC)
+    finally:
+        api.tune(copy_vec_unroll=4, copy_vec_threads=512, copy_cache_mode=0, copy_vec_ctas_sm=4)
+
+
+def test_tiny_grids_cover_everything(stream):
+    # one CTA (and an odd CTA count) must still walk the whole buffer
+    n = 5 * MiB + 999
+    src_h = oracle.random_bytes(n, seed=7)
+    s, d = api.DeviceBuffer(n + 64), api.DeviceBuffer(n + 64)
+    to_device(stream, s, src_h)
+    for path, ctas, so, do in [(VEC, 1, 0, 0), (VEC, 3, 1, 0), (TMA, 1, 16, 32), (TMA, 5, 0, 0)]:
+        to_device(stream, d, np.zeros(n + 64, np.uint8))
+        _copy(stream, d.ptr + do, s.ptr + so, n - 64, path, ctas)
+        got = to_host(stream, d, n + 64)
+        assert np.array_equal(got[do:do + n - 64], src_h[so:so + n - 64])
+        assert not got[:do].any() and not got[do + n - 64:].any()
+    s.free()
+    d.free()
+
+
+@pytest.mark.parametrize("case", [c for c in GOLDEN["cases"] if "dst_sha256" in c], ids=lambda c: str(c["size"]))
+def test_reference_golden_vectors(stream, case):
+    # same seeded source the reference copied on the host when the golden file was made
+    n = case["size"]
+    src_h = oracle.random_bytes(n, seed=GOLDEN["seed"])
+    s, d = api.DeviceBuffer(n + 16), api.DeviceBuffer(n + 16)
+    to_device(stream, s, src_h)
+    to_device(stream, d, np.zeros(n + 16, np.uint8))
+    _copy(stream, d.ptr, s.ptr, n)
+    got = to_host(stream, d, n + 16)
+    assert hashlib.sha256(got[:n].tobytes()).hexdigest() == case["dst_sha256"]
+    assert not got[n:].any()
+    s.free()
+    d.free()
+
+
+def test_device_helpers_agree_with_oracle(stream):
+    n = 3 * MiB + 5
+    buf, res = api.DeviceBuffer(n + 8), api.DeviceBuffer(16)
+    scratch, out = api.DeviceBuffer(api.lib.lcb_checksum_scratch_bytes()), api.DeviceBuffer(8)
+    api.lcb_check(api.lib.lcb_fill_splitmix64(buf.ptr, n, 11, stream.native), "fill")
+    got = to_host(stream, buf, n)
+    want = oracle.random_bytes(n, seed=11)
+    assert np.array_equal(got, want)
+    for m in (n, n - 5, 8, 3, 4096):
+        assert device_checksum(stream, buf.ptr, m, scratch, out) == oracle.checksum64(want[:m])
+        assert device_checksum(stream, buf.ptr, m, scratch, out) == oracle.checksum64(want[:m])  # scratch is reusable
+    other = api.DeviceBuffer(n + 8)
+    to_device(stream, other, want)
+    assert device_compare(stream, buf.ptr, other.ptr, n, res) == (0, 2**64 - 1)
+    planted = want.copy()
+    planted[[100, 4097, n - 1]] ^= 0x40
+    to_device(stream, other, planted)
+    assert device_compare(stream, buf.ptr, other.ptr, n, res) == (3, 100)
+    assert device_compare(stream, buf.ptr + 3, other.ptr + 3, n - 3, res) == (3, 97)   # misaligned operands
+    for b in (buf, res, scratch, out, other):
+        b.free()
+
+
+SWEEP_OFFSETS = [0, 1, 3, 7, 64]
+
+
+def _sweep(stream, sizes, pairs):
+    """DtoD sweep with everything verified on the device: seeded source (seed 1), compare against the
+    source range, guard bands either side of the destination, and checksum(src) == checksum(dst)."""
+    top = max(sizes)
+    src = api.DeviceBuffer(top + 128)
+    dst = api.DeviceBuffer(top + 128 + 2 * GUARD)
+    res, out = api.DeviceBuffer(16), api.DeviceBuffer(8)
+    scratch = api.DeviceBuffer(api.lib.lcb_checksum_scratch_bytes())
+    guard = api.DeviceBuffer(GUARD)
+    stream.memset_d8(guard, GUARD_BYTE, GUARD)
+    stream.run()
+    api.lcb_check(api.lib.lcb_fill_splitmix64(src.ptr, top + 128, 1, stream.native), "fill")
+    for n in sizes:
+        for so, do in pairs:
+            d = dst.ptr + GUARD + do
+            stream.memset_d8(dst.view(do, n + 2 * GUARD), GUARD_BYTE, n + 2 * GUARD)
+            stream.run()
+            api.lcb_check(api.lib.lcb_copy_d2d(d, src.ptr + so, n, stream.native), "lcb_copy_d2d")
+            assert device_compare(stream, d, src.ptr + so, n, res)[0] == 0, (n, so, do)
+            assert device_compare(stream, d - GUARD, guard.ptr, GUARD, res)[0] == 0, ("front guard", n, so, do)
+            assert device_compare(stream, d + n, guard.ptr, GUARD, res)[0] == 0, ("back guard", n, so, do)
+        # 8-byte aligned pair for the checksum property
+        api.lcb_check(api.lib.lcb_copy_d2d(dst.ptr + GUARD, src.ptr + 64, n, stream.native), "lcb_copy_d2d")
+        assert device_checksum(stream, dst.ptr + GUARD, n, scratch, out) == device_checksum(stream, src.ptr + 64, n, scratch, out)
+    assert api.device_error_word() == 0
+    for b in (src, dst, res, out, scratch, guard):
+        b.free()
+
+
+def test_dtod_sweep_powers_of_two_all_offset_pairs(stream):
+    # 4 KiB ... 1 GiB, src/dst offsets {0,1,3,7,64}^2
+    _sweep(stream, [1 << k for k in range(12, 31)], [(a, b) for a in SWEEP_OFFSETS for b in SWEEP_OFFSETS])
+
+
+def test_dtod_sweep_largest_sizes(stream):
+    # 2, 4 and 8 GiB: 64-bit offsets everywhere (the reference over-launches from 256 MiB on)
+    _sweep(stream, [1 << 31, 1 << 32, 1 << 33], [(0, 0), (1, 0), (0, 3), (7, 64), (64, 64)])
