@@ -25,7 +25,8 @@ enum lcbCopyPath {
     LCB_COPY_AUTO = 0,  /* pick by size and alignment                                             */
     LCB_COPY_VEC = 1,   /* 16/32-byte vector loads+stores; src realigned by warp shuffle if needed */
     LCB_COPY_TMA = 2,   /* cp.async.bulk global->smem->global ring; needs (src-dst) % 16 == 0       */
-    LCB_COPY_SMALL = 3  /* single small CTA wave, latency path                                     */
+    LCB_COPY_SMALL = 3, /* single small CTA wave, latency path                                     */
+    LCB_COPY_VEC32 = 4  /* 32-byte vector loads+stores; needs (src-dst) % 32 == 0                   */
 };
 
 /* Device-to-device copy of `bytes` bytes, any alignment, any size (64-bit offsets).  Buffers must not
@@ -90,7 +91,8 @@ int lcb_device_error_word(unsigned int *out);
 const char *lcb_version(void);
 
 /* Override one launch tunable by name (thread counts, unroll, bulk-ring depth ...; the names are the
- * fields of the Tuning record in the kernel sources).  For sweeps; returns 1 for an unknown name. */
+ * fields of the Tuning record in the kernel sources; "reset" restores the shipped configuration).
+ * For sweeps; returns 1 for an unknown name. */
 int lcb_tune(const char *name, int value);
 
 /* CUDA-event stopwatch on a raw stream: start/stop record events on `stream`, elapsed waits for the

@@ -295,6 +295,10 @@ def tune(**knobs):
         lcb_check(lib.lcb_tune(k.encode(), int(v)), f"lcb_tune({k})")
 
 
+def tune_reset():
+    lcb_check(lib.lcb_tune(b"reset", 0), "lcb_tune(reset)")
+
+
 class Timer:
     """CUDA-event stopwatch on a raw stream (lcb_timer_*)."""
 

@@ -22,11 +22,15 @@ struct Tuning {
     int tma_lookahead;      // loads in flight ahead of the store
     int tma_ctas_sm;        // CTAs per SM of the bulk ring kernels
     int tma_cache_hint;     // 0: none  1: evict_first policy on loads and stores
-    int auto_tma_min_bytes; // LCB_COPY_AUTO uses the bulk ring from this size on (mutually aligned only)
+    int auto_tma_min_mib;   // LCB_COPY_AUTO uses the bulk ring from this many MiB on (congruent pointers only; -1 never)
     int memset_path;        // 0 auto, 1 vector, 2 bulk
     int memset_unroll;
     int memset_threads;
     int memset_ctas_sm;
+    int memset_chunk;        // bytes per bulk store of the bulk memset
+    int memset_issuers;      // warps per CTA issuing bulk stores
+    int memset_bulk_ctas_sm; // CTAs per SM of the bulk memset
+    int memset_cache_hint;   // evict_first policy on the bulk stores
 };
 Tuning &tuning();
 

@@ -133,6 +133,58 @@ __global__ void __launch_bounds__(512) copy_vec_kernel(uint4 *__restrict__ dstv,
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// 32-byte vector path (sm_100 256-bit global accesses with an L2 evict_first priority)
+// ---------------------------------------------------------------------------------------------
+struct V8 {
+    uint32_t r[8];
+};
+
+__device__ __forceinline__ V8 ld_v8(const void *p) {
+    V8 v;
+    asm volatile("ld.global.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v.r[0]), "=r"(v.r[1]), "=r"(v.r[2]), "=r"(v.r[3]), "=r"(v.r[4]), "=r"(v.r[5]), "=r"(v.r[6]),
+                   "=r"(v.r[7])
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void st_v8(void *p, const V8 &v) {
+    asm volatile("st.global.L1::no_allocate.L2::evict_first.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 :: "l"(p), "r"(v.r[0]), "r"(v.r[1]), "r"(v.r[2]), "r"(v.r[3]), "r"(v.r[4]), "r"(v.r[5]), "r"(v.r[6]),
+                    "r"(v.r[7])
+                 : "memory");
+}
+
+// Both bodies 32-byte aligned; n32 32-byte vectors; edges (< 32 bytes each side) by the first two warps of CTA 0.
+template <int U>
+__global__ void __launch_bounds__(512) copy_vec32_kernel(uint8_t *__restrict__ dst, const uint8_t *__restrict__ src,
+                                                         size_t n32, Edges e) {
+    if (blockIdx.x == 0) copy_edges(e, threadIdx.x);
+    const int lane = threadIdx.x & 31;
+    const size_t warps_total = (size_t)gridDim.x * (blockDim.x >> 5);
+    const size_t gwarp = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    constexpr size_t TILE = (size_t)U * 32;
+    const size_t ntiles = (n32 + TILE - 1) / TILE;
+    for (size_t t = gwarp; t < ntiles; t += warps_total) {
+        const size_t base = t * TILE;
+        V8 v[U];
+        if (base + TILE <= n32) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) v[u] = ld_v8(src + (base + u * 32 + lane) * 32);
+#pragma unroll
+            for (int u = 0; u < U; ++u) st_v8(dst + (base + u * 32 + lane) * 32, v[u]);
+        } else {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const size_t j = base + u * 32 + lane;
+                if (j < n32) st_v8(dst + j * 32, ld_v8(src + j * 32));
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // bulk-copy ring
 // ---------------------------------------------------------------------------------------------
@@ -333,6 +385,32 @@ int launch_vec(const Split &sp, int ctas, bool small, cudaStream_t st) {
     }
 }
 
+
+int launch_vec32(void *dst, const void *src, size_t bytes, int ctas, cudaStream_t st) {
+    const Tuning &tu = tuning();
+    uint8_t *d = static_cast<uint8_t *>(dst);
+    const uint8_t *s = static_cast<const uint8_t *>(src);
+    size_t head = (32 - (reinterpret_cast<uintptr_t>(d) & 31)) & 31;
+    if (head > bytes) head = bytes;
+    const size_t n32 = (bytes - head) / 32;
+    Edges e;
+    e.dst = d;
+    e.src = s;
+    e.head = (int)head;
+    e.tail = (int)(bytes - head - n32 * 32);
+    e.tail_off = head + n32 * 32;
+    const int threads = tu.copy_vec_threads;
+    const int unroll = tu.copy_vec_unroll >= 4 ? 4 : 2;
+    const size_t per_cta = (size_t)unroll * threads;
+    size_t need = (n32 + per_cta - 1) / per_cta;
+    if (need == 0) need = 1;
+    size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * tu.copy_vec_ctas_sm * (512 / threads);
+    const int grid = (int)(need < cap ? need : cap);
+    if (unroll == 4) copy_vec32_kernel<4><<<grid, threads, 0, st>>>(d + head, s + head, n32, e);
+    else copy_vec32_kernel<2><<<grid, threads, 0, st>>>(d + head, s + head, n32, e);
+    return check_launch();
+}
+
 template <int S, int L>
 int launch_tma_cfg(bool hint, int grid, size_t smem, cudaStream_t st, uint8_t *d, const uint8_t *s, size_t body,
                    uint32_t chunk, const Edges &e) {
@@ -392,7 +470,7 @@ extern "C" int lcb_copy_d2d_ex(void *dst, const void *src, size_t bytes, int pat
     if (path == LCB_COPY_AUTO) {
         const Tuning &tu = tuning();
         if (bytes < 64 * 1024) path = LCB_COPY_SMALL;
-        else if (mutual && tu.auto_tma_min_bytes >= 0 && bytes >= (size_t)tu.auto_tma_min_bytes) path = LCB_COPY_TMA;
+        else if (mutual && tu.auto_tma_min_mib >= 0 && bytes >= ((size_t)tu.auto_tma_min_mib << 20)) path = LCB_COPY_TMA;
         else path = LCB_COPY_VEC;
     }
     switch (path) {
@@ -401,6 +479,9 @@ extern "C" int lcb_copy_d2d_ex(void *dst, const void *src, size_t bytes, int pat
         case LCB_COPY_TMA:
             if (!mutual) return 1;
             return launch_tma(sp, ctas, st);
+        case LCB_COPY_VEC32:
+            if (((reinterpret_cast<uintptr_t>(dst) ^ reinterpret_cast<uintptr_t>(src)) & 31) != 0) return 1;
+            return launch_vec32(dst, src, bytes, ctas, st);
         default: return 1;
     }
 }

@@ -4,7 +4,7 @@
 // fixtures tests/indexing/write_float.cu:1-4 (one scalar store per thread over a 1-D grid) and
 // tests/write_float/write_float.cu:1-7.  Here:
 //  * memset_vec_kernel   persistent grid of 16-byte streaming stores, U stores per lane per iteration.
-//  * memset_bulk_kernel  fills ONE shared-memory tile with the pattern, then a single thread replays it
+//  * memset_bulk_kernel  fills ONE shared-memory tile with the pattern, then one thread per warp replays it
 //                        with bulk stores (cp.async.bulk shared->global); the SM issues one instruction
 //                        per `chunk` bytes written.
 //  * index_fill_kernel   out[i] = float(i), four consecutive elements per 16-byte store.
@@ -51,25 +51,28 @@ __global__ void __launch_bounds__(512) memset_vec_kernel(uint4 *__restrict__ dst
     }
 }
 
-// blockDim = 128.  All threads fill the tile, thread 0 issues the bulk stores.  The tile is never
-// rewritten, so no store has to be waited for until the end.
+// blockDim = 32 * issuers.  All threads fill the tile; lane 0 of every warp then issues bulk stores of the
+// same tile for its share of the chunks (several issuers per SM keep the store queue full).  The tile is
+// never rewritten, so no store has to be waited for until the end.
 template <bool HINT>
-__global__ void __launch_bounds__(128) memset_bulk_kernel(uint8_t *__restrict__ body_dst, size_t body, uint32_t chunk,
+__global__ void __launch_bounds__(256) memset_bulk_kernel(uint8_t *__restrict__ body_dst, size_t body, uint32_t chunk,
                                                           FillEdges e) {
     extern __shared__ __align__(128) uint8_t smem[];
     if (blockIdx.x == 0) fill_edges(e, threadIdx.x);
     const size_t nchunks = (body + chunk - 1) / chunk;
-    if ((size_t)blockIdx.x >= nchunks) return;
+    const size_t issuers = blockDim.x >> 5;
+    if ((size_t)blockIdx.x * issuers >= nchunks) return;
     const uint4 p = make_uint4(e.pattern, e.pattern, e.pattern, e.pattern);
     uint4 *tile = reinterpret_cast<uint4 *>(smem);
     for (uint32_t i = threadIdx.x; i < chunk / 16; i += blockDim.x) tile[i] = p;
     fence_generic_to_async_smem();
     __syncthreads();
-    if (threadIdx.x != 0) return;
+    if ((threadIdx.x & 31) != 0) return;
     uint64_t pol = 0;
     if (HINT) pol = policy_evict_first();
     const uint32_t tile_addr = smem_addr(smem);
-    for (size_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+    const size_t stride = (size_t)gridDim.x * issuers;
+    for (size_t c = (size_t)blockIdx.x * issuers + (threadIdx.x >> 5); c < nchunks; c += stride) {
         const size_t off = c * (size_t)chunk;
         const size_t rem = body - off;
         bulk_s2g<HINT>(body_dst + off, tile_addr, (uint32_t)(rem < chunk ? rem : chunk), pol);
@@ -178,22 +181,27 @@ int memset_any(void *dst, uint32_t pattern, int elem, size_t count, int path, in
     uint8_t *body = e.dst + head;
     const Tuning &tu = tuning();
     if (path == 0) path = tu.memset_path;
-    if (path == 0) path = (bytes >= (size_t)(8u << 20)) ? 2 : 1;
+    if (path == 0) path = 1;  // vector stores measured faster than the bulk replay at every size
     if (path == 2) {
-        const uint32_t chunk = (uint32_t)tu.tma_chunk;
+        const uint32_t chunk = (uint32_t)tu.memset_chunk;
         if (chunk < 1024 || chunk > 65536 || (chunk & 127)) return 1;
+        int issuers = tu.memset_issuers;
+        if (issuers < 2) issuers = 2;  // two warps are needed for the edge bytes
+        if (issuers > 8) issuers = 8;
+        const int bthreads = 32 * issuers;
         const size_t nchunks = (nvec * 16 + chunk - 1) / chunk;
-        size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * tu.memset_ctas_sm;
-        const int grid = (int)(nchunks < cap ? (nchunks ? nchunks : 1) : cap);
+        const size_t need = (nchunks + issuers - 1) / issuers;
+        size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * tu.memset_bulk_ctas_sm;
+        const int grid = (int)(need < cap ? (need ? need : 1) : cap);
         cudaError_t err;
-        if (tu.tma_cache_hint) {
+        if (tu.memset_cache_hint) {
             err = cudaFuncSetAttribute(memset_bulk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)chunk);
             if (err != cudaSuccess) return (int)err;
-            memset_bulk_kernel<true><<<grid, 128, chunk, st>>>(body, nvec * 16, chunk, e);
+            memset_bulk_kernel<true><<<grid, bthreads, chunk, st>>>(body, nvec * 16, chunk, e);
         } else {
             err = cudaFuncSetAttribute(memset_bulk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)chunk);
             if (err != cudaSuccess) return (int)err;
-            memset_bulk_kernel<false><<<grid, 128, chunk, st>>>(body, nvec * 16, chunk, e);
+            memset_bulk_kernel<false><<<grid, bthreads, chunk, st>>>(body, nvec * 16, chunk, e);
         }
         return check_launch();
     }

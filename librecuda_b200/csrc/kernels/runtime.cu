@@ -7,23 +7,29 @@
 
 namespace lcb {
 
-Tuning &tuning() {
-    static Tuning t = {
+static const Tuning kDefaults = {
         /*copy_vec_threads*/ 512,
         /*copy_vec_unroll*/ 4,
-        /*copy_vec_ctas_sm*/ 4,
-        /*copy_cache_mode*/ 0,
-        /*tma_chunk*/ 16384,
+        /*copy_vec_ctas_sm*/ 1,
+        /*copy_cache_mode*/ 2,
+        /*tma_chunk*/ 8192,
         /*tma_stages*/ 8,
-        /*tma_lookahead*/ 4,
+        /*tma_lookahead*/ 6,
         /*tma_ctas_sm*/ 1,
         /*tma_cache_hint*/ 0,
-        /*auto_tma_min_bytes*/ -1,
+        /*auto_tma_min_mib*/ 512,
         /*memset_path*/ 0,
         /*memset_unroll*/ 8,
-        /*memset_threads*/ 512,
+        /*memset_threads*/ 256,
         /*memset_ctas_sm*/ 4,
-    };
+        /*memset_chunk*/ 32768,
+        /*memset_issuers*/ 4,
+        /*memset_bulk_ctas_sm*/ 2,
+        /*memset_cache_hint*/ 0,
+};
+
+Tuning &tuning() {
+    static Tuning t = kDefaults;
     return t;
 }
 
@@ -46,6 +52,10 @@ int check_launch() { return (int)cudaGetLastError(); }
 extern "C" int lcb_tune(const char *name, int value) {
     using lcb::tuning;
     if (name == nullptr) return 1;
+    if (std::strcmp(name, "reset") == 0) {  // back to the shipped configuration
+        tuning() = lcb::kDefaults;
+        return 0;
+    }
 #define LCB_KNOB(field)                  \
     if (std::strcmp(name, #field) == 0) { \
         tuning().field = value;          \
@@ -60,11 +70,15 @@ extern "C" int lcb_tune(const char *name, int value) {
     LCB_KNOB(tma_lookahead)
     LCB_KNOB(tma_ctas_sm)
     LCB_KNOB(tma_cache_hint)
-    LCB_KNOB(auto_tma_min_bytes)
+    LCB_KNOB(auto_tma_min_mib)
     LCB_KNOB(memset_path)
     LCB_KNOB(memset_unroll)
     LCB_KNOB(memset_threads)
     LCB_KNOB(memset_ctas_sm)
+    LCB_KNOB(memset_chunk)
+    LCB_KNOB(memset_issuers)
+    LCB_KNOB(memset_bulk_ctas_sm)
+    LCB_KNOB(memset_cache_hint)
 #undef LCB_KNOB
     return 1;
 }

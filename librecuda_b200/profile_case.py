@@ -1,0 +1,67 @@
+"""Runs ONE kernel of the library a few times on a small, fixed case -- the command to put under a profiler.
+
+    python -m librecuda_b200.profile_case copy   [--bytes N] [--reps R] [--path auto|vec|tma|vec32] [--src-off A] [--dst-off B]
+    python -m librecuda_b200.profile_case memset [--bytes N] [--reps R] [--path auto|vec|bulk]
+    python -m librecuda_b200.profile_case index_fill | axpb | checksum | alltoall_self
+
+The default 256 MiB per buffer is larger than the 126 MB L2 (DRAM counters stay meaningful) and small
+enough for a multi-pass capture to finish in about a minute.  Prints the CUDA-event time per launch.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+
+from . import api
+
+PATHS = {"auto": 0, "vec": 1, "tma": 2, "small": 3, "vec32": 4}
+MEMSET_PATHS = {"auto": 0, "vec": 1, "bulk": 2}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["copy", "memset", "index_fill", "axpb", "checksum", "alltoall_self"])
+    ap.add_argument("--bytes", type=int, default=256 << 20)
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--path", default="auto")
+    ap.add_argument("--src-off", type=int, default=0)
+    ap.add_argument("--dst-off", type=int, default=0)
+    args = ap.parse_args()
+    lib = api.lib
+    api.Context(0)
+    st = api.Stream()
+    nat = st.native
+    n = args.bytes
+    a, b = api.DeviceBuffer(n + 4096), api.DeviceBuffer(n + 4096)
+    api.lcb_check(lib.lcb_fill_splitmix64(a.ptr, n + 4096, 1, nat), "fill")
+    st.memset_d8(b, 0, n + 4096)
+    st.run()
+    scratch, out = api.DeviceBuffer(lib.lcb_checksum_scratch_bytes()), api.DeviceBuffer(8)
+    peers = (C.c_void_p * 2)(b.ptr, b.ptr + (n // 32) * 16)
+
+    def launch():
+        if args.kernel == "copy":
+            return lib.lcb_copy_d2d_ex(b.ptr + args.dst_off, a.ptr + args.src_off, n, PATHS[args.path], 0, nat)
+        if args.kernel == "memset":
+            return lib.lcb_memset_ex(b.ptr, 0x40490FDB, 4, n // 4, MEMSET_PATHS[args.path], 0, nat)
+        if args.kernel == "index_fill":
+            return lib.lcb_index_fill_f32(b.ptr, n // 4, nat)
+        if args.kernel == "axpb":
+            return lib.lcb_axpb_f32(b.ptr, a.ptr, 2.0, 1.0, n // 4, nat)
+        if args.kernel == "checksum":
+            return lib.lcb_checksum64(a.ptr, n, scratch.ptr, out.ptr, nat)
+        # two "ranks" folded onto one GPU: both halves of the send buffer land in this GPU's memory
+        return lib.lcb_alltoall_push(peers, a.ptr, (n // 64) * 16, 2, 0, nat)
+
+    t = api.Timer()
+    for _ in range(args.reps):
+        t.start(nat)
+        api.lcb_check(launch(), args.kernel)
+        t.stop(nat)
+        print(f"{args.kernel} {args.path} {n} bytes: {t.elapsed_ms():.4f} ms")
+    assert api.device_error_word() == 0
+    t.destroy()
+
+
+if __name__ == "__main__":
+    main()

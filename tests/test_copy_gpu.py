@@ -14,7 +14,7 @@ from gpu_util import GUARD, GUARD_BYTE, device_checksum, device_compare, to_devi
 
 pytestmark = pytest.mark.gpu
 MiB = 1 << 20
-AUTO, VEC, TMA, SMALL = 0, 1, 2, 3
+AUTO, VEC, TMA, SMALL, VEC32 = 0, 1, 2, 3, 4
 GOLDEN = json.loads((Path(__file__).parent / "golden" / "ref_d2d_golden.json").read_text())
 
 
@@ -87,7 +87,14 @@ def test_bulk_path_edges_and_small_bodies(stream):
 def test_bulk_path_rejects_mutually_misaligned(stream):
     a = api.DeviceBuffer(4096)
     assert api.lib.lcb_copy_d2d_ex(a.ptr + 1, a.ptr + 2048, 64, TMA, 0, stream.native) == 1
+    assert api.lib.lcb_copy_d2d_ex(a.ptr + 16, a.ptr + 2048, 64, VEC32, 0, stream.native) == 1
     a.free()
+
+
+def test_32_byte_vector_path(stream):
+    cases = [(n, o, o + 32 * k) for n in (0, 1, 31, 32, 33, 63, 65, 1000, 4096, 65536 + 9, 5 * MiB + 77, 33 * MiB)
+             for o in (0, 1, 16, 31) for k in (0, 3)]
+    _run_cases(stream, cases, VEC32)
 
 
 @pytest.mark.parametrize("knobs", [dict(tma_stages=4, tma_lookahead=2, tma_chunk=8192),
@@ -100,7 +107,7 @@ def test_bulk_ring_configurations(stream, knobs):
         api.tune(**knobs)
         _run_cases(stream, [(n, o, o) for n in (5 * MiB + 48, 333333, 65536 * 7) for o in (0, 16)], TMA)
     finally:
-        api.tune(tma_stages=8, tma_lookahead=4, tma_chunk=16384, tma_ctas_sm=1, tma_cache_hint=0)
+        api.tune_reset()
 
 
 @pytest.mark.parametrize("knobs", [dict(copy_vec_unroll=1), dict(copy_vec_unroll=2), dict(copy_vec_unroll=8),
@@ -111,7 +118,7 @@ def test_vector_kernel_configurations(stream, knobs):
         api.tune(**knobs)
         _run_cases(stream, [(n, so, do) for n in (9 * MiB + 77, 123457) for so, do in [(0, 0), (3, 0), (0, 9), (64, 6)]], VEC)
     finally:
-        api.tune(copy_vec_unroll=4, copy_vec_threads=512, copy_cache_mode=0, copy_vec_ctas_sm=4)
+        api.tune_reset()
 
 
 def test_tiny_grids_cover_everything(stream):

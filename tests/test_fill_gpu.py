@@ -48,6 +48,19 @@ def test_memset_mid_and_large(stream, path):
     _memset_cases(stream, cases, path)
 
 
+@pytest.mark.parametrize("knobs", [dict(memset_chunk=65536, memset_issuers=2, memset_bulk_ctas_sm=3),
+                                   dict(memset_chunk=8192, memset_issuers=8, memset_bulk_ctas_sm=1, memset_cache_hint=1),
+                                   dict(memset_chunk=16384, memset_issuers=1, memset_bulk_ctas_sm=4),
+                                   dict(memset_threads=512, memset_unroll=2, memset_ctas_sm=1)])
+def test_memset_configurations(stream, knobs):
+    try:
+        api.tune(**knobs)
+        for path in (1, 2):
+            _memset_cases(stream, [(1, 0x3C, 7 * MiB + 5, 3), (4, 0xCAFEF00D, 2 * MiB + 1, 8), (2, 0xA55A, 70001, 2)], path)
+    finally:
+        api.tune_reset()
+
+
 def test_memset_rejects_misaligned_elements(stream):
     d = api.DeviceBuffer(4096)
     assert api.lib.lcb_memset_d32(d.ptr + 2, 1, 4, stream.native) == 1
