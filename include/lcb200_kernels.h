@@ -83,6 +83,21 @@ int lcb_compare_bytes(const void *a, const void *b, size_t bytes, uint64_t *resu
 int lcb_checksum64(const void *src, size_t bytes, uint64_t *scratch, uint64_t *out, lcbStream stream);
 size_t lcb_checksum_scratch_bytes(void);
 
+/* lcb_checksum64 for callers that cannot allocate device memory.  No counterpart in the reference.
+ * Same result as lcb_checksum64, but the scratch (one ticket counter + 1024 partial sums, about 8 KiB) is a
+ * fixed array compiled into the library, so nothing is allocated here or by the caller: meant for a check
+ * that runs when the application's own pool already owns all free HBM, or from code that sits inside a
+ * stream capture, where allocating calls are refused.  Limits and rules:
+ *   - `bytes` above lcb_checksum64_noalloc_max_bytes() (64 GiB) is rejected with 1 and a line on stderr;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
+ *     first call before any stream capture begins;
+ *   - every call on a device shares the one array (it is re-zeroed where needed at the start of a call), so
+ *     two calls that may run at the same time on the GPU -- different streams, no ordering -- race: order them;
+ *   - each GPU that loads the library holds the array until the process exits.
+ * src 8-byte aligned; `out` is device memory for one uint64_t. */
+int lcb_checksum64_noalloc(const void *src, size_t bytes, uint64_t *out, lcbStream stream);
+size_t lcb_checksum64_noalloc_max_bytes(void);
+
 /* Reads and clears the per-device sticky word that kernels set when a bounded wait (mbarrier) gave
  * up: 0 = no error.  Synchronises the device. */
 int lcb_device_error_word(unsigned int *out);

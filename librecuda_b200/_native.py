@@ -37,6 +37,8 @@ LCB_FUNCTIONS = {
     "lcb_compare_bytes": (i32, [vp, vp, sz, vp, vp]),
     "lcb_checksum64": (i32, [vp, sz, vp, vp, vp]),
     "lcb_checksum_scratch_bytes": (sz, []),
+    "lcb_checksum64_noalloc": (i32, [vp, sz, vp, vp]),
+    "lcb_checksum64_noalloc_max_bytes": (sz, []),
     "lcb_device_error_word": (i32, [C.POINTER(C.c_uint)]),
     "lcb_version": (C.c_char_p, []),
     "lcb_tune": (i32, [C.c_char_p, i32]),

@@ -2,6 +2,8 @@
 // They let full-size parity checks (multi-GiB buffers) run at HBM speed instead of over PCIe.
 // No counterpart in the reference, whose tests compare on the host after a DtoH copy
 // (tests/dma_chronological_consistency/main.cpp:73-85).
+#include <cstdio>
+
 #include "common.cuh"
 #include "lcb200_kernels.h"
 
@@ -155,5 +157,71 @@ extern "C" int lcb_checksum64(const void *src, size_t bytes, uint64_t *scratch, 
                                               static_cast<const uint8_t *>(src) + nwords * 8, (int)(bytes - nwords * 8),
                                               reinterpret_cast<unsigned long long *>(scratch),
                                               reinterpret_cast<unsigned long long *>(out));
+    return check_launch();
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Checksum without any allocation
+// ---------------------------------------------------------------------------------------------------
+// Some users of this checksum are not in a position to get scratch memory: a verification pass that runs
+// after the application has handed every free byte of HBM to its own pool (the 8 GiB-shard copies this
+// library is built for are usually checked exactly then), or a host that is between cudaStreamBeginCapture
+// and EndCapture, where an allocating call is an error.  For them the ticket counter and the per-CTA
+// partial sums live in this fixed array inside the library image instead of a caller-supplied buffer.
+// Every GPU that loads the library carries these bytes until the process exits.
+constexpr int kStaticChecksumCtas = 1024;                           // partial-sum slots
+constexpr size_t kStaticChecksumMaxBytes = (size_t)64 << 30;        // largest input one call accepts (64 GiB)
+static __device__ __align__(256) unsigned long long g_static_checksum_scratch[1 + kStaticChecksumCtas];
+
+namespace {
+// Device address of the array, looked up once per device.  In host code the array's name only stands for
+// the symbol; a kernel must be given the address cudaGetSymbolAddress reports for the CURRENT device.
+unsigned long long *static_scratch_for_current_device(cudaError_t *err) {
+    static unsigned long long *addr[64] = {};
+    int dev = -1;
+    *err = cudaGetDevice(&dev);
+    if (*err != cudaSuccess) return nullptr;
+    if (dev < 0 || dev >= 64) {
+        *err = cudaErrorInvalidDevice;
+        return nullptr;
+    }
+    if (addr[dev] == nullptr) {
+        void *p = nullptr;
+        *err = cudaGetSymbolAddress(&p, g_static_checksum_scratch);
+        if (*err != cudaSuccess) return nullptr;
+        addr[dev] = static_cast<unsigned long long *>(p);
+    }
+    return addr[dev];
+}
+}  // namespace
+
+extern "C" size_t lcb_checksum64_noalloc_max_bytes(void) { return kStaticChecksumMaxBytes; }
+
+extern "C" int lcb_checksum64_noalloc(const void *src, size_t bytes, uint64_t *out, lcbStream stream) {
+    using namespace lcb;
+    if (src == nullptr || out == nullptr) return 1;
+    if (reinterpret_cast<uintptr_t>(src) & 7) return 1;
+    if (bytes > kStaticChecksumMaxBytes) {
+        fprintf(stderr, "lcb_checksum64_noalloc: %zu bytes exceed the %zu-byte limit of the built-in scratch; "
+                        "use lcb_checksum64 with caller-provided scratch\n", bytes, kStaticChecksumMaxBytes);
+        return 1;
+    }
+    cudaError_t err = cudaSuccess;
+    unsigned long long *scratch = static_scratch_for_current_device(&err);
+    if (scratch == nullptr) return (int)err;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // the array keeps whatever the previous call left: the ticket counter has to start from zero
+    err = cudaMemsetAsync(scratch, 0, sizeof(unsigned long long), st);
+    if (err != cudaSuccess) return (int)err;
+    const size_t nwords = bytes / 8;
+    const int threads = 512;
+    size_t need = (nwords + threads - 1) / threads;
+    if (need == 0) need = 1;
+    size_t cap = (size_t)sm_count() * 4;
+    if (cap > (size_t)kStaticChecksumCtas) cap = kStaticChecksumCtas;
+    const int grid = (int)(need < cap ? need : cap);
+    checksum_kernel<<<grid, threads, 0, st>>>(static_cast<const uint64_t *>(src), nwords,
+                                              static_cast<const uint8_t *>(src) + nwords * 8, (int)(bytes - nwords * 8),
+                                              scratch, reinterpret_cast<unsigned long long *>(out));
     return check_launch();
 }
