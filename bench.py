@@ -352,18 +352,9 @@ def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_r
     api.lcb_check(lib.lcb_fill_splitmix64(send.ptr, G * chunk, 100 + rank, native), "fill")
     stream.memset_d8(recv, 0, G * chunk)
     stream.run()
-    handle = C.create_string_buffer(72)
-    api.check(lib.libreCuIpcGetMemHandle(handle, recv.ptr), "libreCuIpcGetMemHandle")
-    handles = [None] * G
-    dist.all_gather_object(handles, handle.raw)
-    peers = []
-    for r in range(G):
-        if r == rank:
-            peers.append(recv.ptr)
-        else:
-            p = C.c_void_p()
-            api.check(lib.libreCuIpcOpenMemHandle(C.byref(p), handles[r]), "libreCuIpcOpenMemHandle")
-            peers.append(p.value)
+    from librecuda_b200 import multirank as mr
+
+    peers = mr.open_peers(dist, recv)
     peer_arr = (C.c_void_p * G)(*peers)
     out = {"world": G, "nominal_GBps": NVLINK_NOMINAL, "measured_peer_copy_GBps": NVLINK_MEASURED}
 
@@ -443,9 +434,7 @@ def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_r
     report("broadcast_nccl_4GiB", bsz, ms)
     del tb
     barrier()
-    for r in range(G):
-        if r != rank:
-            api.check(lib.libreCuIpcCloseMemHandle(peers[r]), "libreCuIpcCloseMemHandle")
+    mr.close_peers(dist, peers)
     barrier()
     for b in (send, recv, resb):
         b.free()

@@ -1,0 +1,199 @@
+"""Multi-GPU data movement inside one process (one context per GPU, peer access over NVLink): partitioned
+copy, peer copy in both directions, the fused all-to-all, broadcast -- own kernels and the NCCL variants --
+all bit-exact against the oracle's host models.  Needs at least two GPUs."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import oracle
+from librecuda_b200 import api
+
+pytestmark = pytest.mark.gpu
+MiB = 1 << 20
+lib = api.lib
+
+
+@pytest.fixture(scope="module")
+def gpus(ctx, gpu_count):
+    if gpu_count < 2:
+        pytest.skip("needs >= 2 GPUs")
+    n = min(gpu_count, 4)
+    ctxs = [ctx] + [api.Context(i) for i in range(1, n)]
+    for c in ctxs:
+        c.set_current()
+        for peer in ctxs:
+            if peer is not c:
+                can = C.c_int()
+                api.check(lib.libreCuDeviceCanAccessPeer(C.byref(can), c.device, peer.device))
+                assert can.value == 1
+                c.enable_peer_access(peer)
+                c.enable_peer_access(peer)  # idempotent
+    streams = []
+    for c in ctxs:
+        c.set_current()
+        streams.append(api.Stream())
+    ctxs[0].set_current()
+    yield ctxs, streams
+    for s in streams:
+        s.destroy()
+    ctxs[0].set_current()
+
+
+def _alloc_on(c, nbytes):
+    c.set_current()
+    return api.DeviceBuffer(nbytes)
+
+
+def _upload(ctxs, streams, g, buf, host):
+    ctxs[g].set_current()
+    streams[g].memcpy(buf, host, host.nbytes)
+    streams[g].run()
+
+
+def _download(ctxs, streams, g, buf, nbytes):
+    ctxs[g].set_current()
+    out = np.empty(nbytes, np.uint8)
+    streams[g].memcpy(out, buf, nbytes)
+    streams[g].run()
+    return out
+
+
+@pytest.mark.parametrize("so,do", [(0, 0), (1, 0), (16, 3)])
+def test_peer_copy_push_and_pull(gpus, so, do):
+    ctxs, streams = gpus
+    n = 9 * MiB + 77
+    src_h = oracle.random_bytes(n + 64, seed=3)
+    a = _alloc_on(ctxs[0], n + 64)
+    b = _alloc_on(ctxs[1], n + 64)
+    _upload(ctxs, streams, 0, a, src_h)
+    _upload(ctxs, streams, 1, b, np.zeros(n + 64, np.uint8))
+    # push: kernel on GPU 0 stores into GPU 1's memory
+    ctxs[0].set_current()
+    api.check(lib.libreCuMemcpyPeer(b.ptr + do, a.ptr + so, n, streams[0].handle, False))
+    streams[0].run()
+    got = _download(ctxs, streams, 1, b, n + 64)
+    assert np.array_equal(got[do:do + n], src_h[so:so + n]) and not got[:do].any() and not got[do + n:].any()
+    # pull: kernel on GPU 1 loads from GPU 0's memory
+    _upload(ctxs, streams, 1, b, np.zeros(n + 64, np.uint8))
+    ctxs[1].set_current()
+    api.check(lib.libreCuMemcpyPeer(b.ptr + do, a.ptr + so, n, streams[1].handle, False))
+    streams[1].run()
+    got = _download(ctxs, streams, 1, b, n + 64)
+    assert np.array_equal(got[do:do + n], src_h[so:so + n])
+    ctxs[0].set_current()
+    a.free()
+    ctxs[1].set_current()
+    b.free()
+    ctxs[0].set_current()
+
+
+def test_partitioned_copy_scatter(gpus):
+    ctxs, streams = gpus
+    G = len(ctxs)
+    total = 41 * MiB + 12345
+    off = oracle.partition(total, G, 2 << 20)
+    src_h = oracle.random_bytes(total, seed=3)
+    src = _alloc_on(ctxs[0], total)
+    _upload(ctxs, streams, 0, src, src_h)
+    dsts = [_alloc_on(ctxs[g], max(off[g + 1] - off[g], 1) + 64) for g in range(G)]
+    for g in range(G):
+        _upload(ctxs, streams, g, dsts[g], np.zeros(dsts[g].nbytes, np.uint8))
+    ctxs[0].set_current()
+    dp = (C.c_void_p * G)(*[d.ptr for d in dsts])
+    # all shards pushed by GPU 0 on separate streams of GPU 0 would share one port; here shard g is PULLED by GPU g
+    sp = (C.c_void_p * G)(*[s.handle for s in streams])
+    api.check(lib.libreCuMemcpyPartitioned(dp, src.ptr, total, G, 0, sp))
+    for s in streams:
+        s.commence()
+    for s in streams:
+        s.await_()
+    for g in range(G):
+        got = _download(ctxs, streams, g, dsts[g], dsts[g].nbytes)
+        n = off[g + 1] - off[g]
+        assert np.array_equal(got[:n], src_h[off[g]:off[g + 1]]) and not got[n:].any()
+    for g in range(G):
+        ctxs[g].set_current()
+        dsts[g].free()
+    ctxs[0].set_current()
+    src.free()
+
+
+@pytest.mark.parametrize("use_nccl", [0, 1])
+def test_all_to_all(gpus, use_nccl):
+    ctxs, streams = gpus
+    G = len(ctxs)
+    chunk = 3 * MiB + 48
+    send_h = [oracle.random_bytes(G * chunk, seed=30 + r) for r in range(G)]
+    want = oracle.alltoall(send_h)
+    send = [_alloc_on(ctxs[g], G * chunk) for g in range(G)]
+    recv = [_alloc_on(ctxs[g], G * chunk) for g in range(G)]
+    for g in range(G):
+        _upload(ctxs, streams, g, send[g], send_h[g])
+        _upload(ctxs, streams, g, recv[g], np.zeros(G * chunk, np.uint8))
+    ctxs[0].set_current()
+    rp = (C.c_void_p * G)(*[b.ptr for b in recv])
+    sp = (C.c_void_p * G)(*[b.ptr for b in send])
+    stp = (C.c_void_p * G)(*[s.handle for s in streams])
+    api.check(lib.libreCuAllToAll(rp, sp, chunk, G, stp, use_nccl))
+    for s in streams:
+        s.await_()
+    for g in range(G):
+        assert np.array_equal(_download(ctxs, streams, g, recv[g], G * chunk), want[g]), f"rank {g}"
+    for g in range(G):
+        ctxs[g].set_current()
+        send[g].free()
+        recv[g].free()
+    ctxs[0].set_current()
+
+
+def test_all_to_all_push_recorded_per_rank(gpus):
+    # the per-rank half is an ordinary recorded stream operation
+    ctxs, streams = gpus
+    G = len(ctxs)
+    chunk = MiB + 16
+    send_h = [oracle.random_bytes(G * chunk, seed=50 + r) for r in range(G)]
+    want = oracle.alltoall(send_h)
+    send = [_alloc_on(ctxs[g], G * chunk) for g in range(G)]
+    recv = [_alloc_on(ctxs[g], G * chunk) for g in range(G)]
+    rp = (C.c_void_p * G)(*[b.ptr for b in recv])
+    for g in range(G):
+        ctxs[g].set_current()
+        streams[g].memcpy(send[g], send_h[g], G * chunk)
+        api.check(lib.libreCuAllToAllPush(rp, send[g].ptr, chunk, G, g, streams[g].handle))
+    for s in streams:
+        s.commence()
+    for s in streams:
+        s.await_()
+    for g in range(G):
+        assert np.array_equal(_download(ctxs, streams, g, recv[g], G * chunk), want[g])
+    assert lib.libreCuAllToAllPush(rp, send[0].ptr, 24, G, 0, streams[0].handle) == api.ERROR_INVALID_VALUE
+    for g in range(G):
+        ctxs[g].set_current()
+        send[g].free()
+        recv[g].free()
+    ctxs[0].set_current()
+
+
+@pytest.mark.parametrize("use_nccl", [0, 1])
+@pytest.mark.parametrize("root", [0, 1])
+def test_broadcast(gpus, use_nccl, root):
+    ctxs, streams = gpus
+    G = len(ctxs)
+    n = 37 * MiB + 1001
+    data = oracle.random_bytes(n, seed=3)
+    bufs = [_alloc_on(ctxs[g], n) for g in range(G)]
+    for g in range(G):
+        _upload(ctxs, streams, g, bufs[g], data if g == root else np.zeros(n, np.uint8))
+    ctxs[0].set_current()
+    bp = (C.c_void_p * G)(*[b.ptr for b in bufs])
+    stp = (C.c_void_p * G)(*[s.handle for s in streams])
+    api.check(lib.libreCuBroadcast(bp, root, n, G, stp, use_nccl))
+    for s in streams:
+        s.await_()
+    for g in range(G):
+        assert np.array_equal(_download(ctxs, streams, g, bufs[g], n), data), f"rank {g}"
+    for g in range(G):
+        ctxs[g].set_current()
+        bufs[g].free()
+    ctxs[0].set_current()
