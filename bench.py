@@ -267,6 +267,14 @@ def run_ours(args):
         also[name] = {"GBps": round(gbps, 1), "ms": round(t_ms, 4), "frac_of_measured_hbm": round(gbps / peak, 4),
                       "frac_of_nominal_8000": round(gbps / 8000.0, 4)}
 
+    for name, fn, nbytes in (("vendor_cudaMemcpyAsync_d2d_1GiB", lambda: api.lcb_check(lib.lcb_vendor_memcpy_d2d(dst.ptr, src.ptr, n, native), "vendor copy"), 2 * n),
+                             ("vendor_cudaMemsetAsync_1GiB", lambda: api.lcb_check(lib.lcb_vendor_memset_d8(dst.ptr, 0xA5, n, native), "vendor memset"), n)):
+        for _ in range(3):
+            fn()
+        barrier()
+        t_ms = timed_loop(api, stream, fn, steps)
+        also[name] = {"GBps": round(nbytes / (t_ms * 1e-3) / 1e9, 1), "ms": round(t_ms, 4), "note": "CUDA runtime's own path, for comparison"}
+
     # end to end through the public API with HOST buffers: HtoD -> DtoD -> DtoH inside the timed region
     e2e = run_e2e(api, ctx, n, max(2, min(steps, 10)), max_over_ranks, barrier, world)
 
@@ -304,43 +312,81 @@ def run_ours(args):
 
 
 def run_e2e(api, ctx, n, steps, max_over_ranks, barrier, world):
-    """The call sequence a user of the API makes (reference tests/memcopy/main.cpp:47-57) on pinned host
-    buffers, timed with the API's own events."""
+    """End to end through the public API on pinned HOST buffers, timed with the API's own events.
+
+    serial:    the call sequence of the reference's tests/memcopy/main.cpp:47-57 on one stream
+               (HtoD 1 GiB -> DtoD -> DtoH 1 GiB).
+    pipelined: the same bytes in 32 MiB pieces dealt round-robin to four streams, so the HtoD of one piece
+               overlaps the DtoD and DtoH of others (PCIe is full duplex); stream 0 joins the others with
+               libreCuStreamWaitEvent before the end event.  This is the reported e2e value."""
     import numpy as np
 
-    st = api.Stream()
+    S, piece = 4, 32 * MiB
+    streams = [api.Stream() for _ in range(S)]
     hin, hout = api.PinnedBuffer(n), api.PinnedBuffer(n)
-    hin.array[:] = np.arange(n, dtype=np.uint8) if n <= (1 << 20) else np.resize(np.arange(251, dtype=np.uint8), n)
+    hin.array[:] = np.resize(np.arange(251, dtype=np.uint8), n)
     a, b = api.DeviceBuffer(n), api.DeviceBuffer(n)
     start, end = api.Event(), api.Event()
+    joins = [api.Event() for _ in range(S)]
 
-    def record_step():
+    def serial_step():
+        st = streams[0]
         st.memcpy(a, hin.array, n)
         st.memcpy(b, a, n)
         st.memcpy(hout.array, b, n)
 
-    record_step()
-    record_step()
-    st.run()
-    barrier()
-    start.record(st)
-    for _ in range(steps):
-        record_step()
-    end.record(st)
-    st.run()
-    ms = api.elapsed_ms(start, end) / steps
-    ok = bool(np.array_equal(hout.array[:: 4099], hin.array[:: 4099]) and np.array_equal(hout.array[-4096:], hin.array[-4096:]))
-    ms = max_over_ranks(ms)
-    for e in (start, end):
+    def pipelined_step():
+        for i, off in enumerate(range(0, n, piece)):
+            st = streams[i % S]
+            m = min(piece, n - off)
+            st.memcpy(a.view(off, m), hin.array[off:off + m], m)
+            st.memcpy(b.view(off, m), a.view(off, m), m)
+            st.memcpy(hout.array[off:off + m], b.view(off, m), m)
+
+    def timed(step_fn, multi_stream):
+        for _ in range(2):
+            step_fn()
+        for st in streams:
+            st.run()
+        barrier()
+        start.record(streams[0])
+        streams[0].commence()
+        if multi_stream:  # the other streams start after the start event
+            for st in streams[1:]:
+                st.wait_event(start)
+        for _ in range(steps):
+            step_fn()
+        if multi_stream:
+            for i in range(1, S):
+                joins[i].record(streams[i])
+                streams[i].commence()
+                streams[0].wait_event(joins[i])
+        end.record(streams[0])
+        streams[0].commence()
+        for st in streams:
+            st.await_()
+        return max_over_ranks(api.elapsed_ms(start, end) / steps)
+
+    hout.array[:] = 0
+    ms_serial = timed(serial_step, False)
+    ok = bool(np.array_equal(hout.array[::4099], hin.array[::4099]) and np.array_equal(hout.array[-4096:], hin.array[-4096:]))
+    hout.array[:] = 0
+    ms_pipe = timed(pipelined_step, True)
+    ok = ok and bool(np.array_equal(hout.array[::4099], hin.array[::4099]) and np.array_equal(hout.array[-4096:], hin.array[-4096:]))
+    for e in [start, end] + joins:
         e.destroy()
     for x in (a, b):
         x.free()
     hin.free()
     hout.free()
-    st.destroy()
-    return {"value": round(world * 2.0 * n / (ms * 1e-3) / 1e9, 2), "unit": UNIT, "h2d_bytes_per_step": n,
-            "d2h_bytes_per_step": n, "ms_per_step": round(ms, 3), "steps": steps, "verified": ok,
-            "path": "libreCuMemCpy HtoD -> DtoD -> DtoH on pinned host buffers, timed with libreCuEvent*"}
+    for st in streams:
+        st.destroy()
+    gbps = lambda ms: round(world * 2.0 * n / (ms * 1e-3) / 1e9, 2)
+    return {"value": gbps(ms_pipe), "unit": UNIT, "h2d_bytes_per_step": n, "d2h_bytes_per_step": n,
+            "ms_per_step": round(ms_pipe, 3), "steps": steps, "verified": ok,
+            "path": "libreCuMemCpy HtoD -> DtoD -> DtoH on pinned host buffers in 32 MiB pieces over 4 streams, "
+                    "timed with libreCuEvent* (PCIe-bound)",
+            "serial_one_stream": {"value": gbps(ms_serial), "ms_per_step": round(ms_serial, 3)}}
 
 
 def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_ranks):

@@ -119,6 +119,11 @@ int lcb_timer_elapsed_ms(void *timer, float *ms_out);
 int lcb_timer_destroy(void *timer);
 int lcb_stream_synchronize(lcbStream stream);
 
+/* The CUDA runtime's own device-to-device copy and memset on the same stream, exported only so that the
+ * benchmark can time them beside this library's kernels.  Nothing in the library calls them. */
+int lcb_vendor_memcpy_d2d(void *dst, const void *src, size_t bytes, lcbStream stream);
+int lcb_vendor_memset_d8(void *dst, unsigned char value, size_t bytes, lcbStream stream);
+
 #ifdef __cplusplus
 }
 #endif

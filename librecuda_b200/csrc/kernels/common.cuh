@@ -31,11 +31,49 @@ struct Tuning {
     int memset_issuers;      // warps per CTA issuing bulk stores
     int memset_bulk_ctas_sm; // CTAs per SM of the bulk memset
     int memset_cache_hint;   // evict_first policy on the bulk stores
+    int pdl;                 // 1: launch with programmatic stream serialization (kernel prologues overlap the
+                             //    tail of the previous kernel on the stream)
+    int copy_vec_smem_pad;   // extra dynamic shared memory per CTA of the vector copy (caps CTAs per SM)
+    int tma_smem_pad;        // same for the bulk ring
+    int memset_smem_pad;     // same for the vector memset
+    int fill_ctas_sm;        // CTAs per SM worth of grid for index fill / axpb
 };
 Tuning &tuning();
 
 int sm_count();            // SMs of the current device (cached per device)
 int check_launch();        // cudaGetLastError() as int
+
+// ---------------------------------------------------------------------------------------------
+// launch helper and programmatic dependent launch
+// ---------------------------------------------------------------------------------------------
+// Kernels call pdl_launch_dependents() first thing and pdl_wait() before their first global access.  When
+// launched with the programmatic-serialization attribute, the CTAs of the NEXT kernel on the stream become
+// resident while this one is still running and start the moment it has completed and flushed; without the
+// attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline int launch_kernel(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t st,
+                         Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(block, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    if (tuning().pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // ---------------------------------------------------------------------------------------------
 // streaming 16-byte accesses

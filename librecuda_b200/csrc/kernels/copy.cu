@@ -70,6 +70,8 @@ __global__ void __launch_bounds__(512) copy_vec_kernel(uint4 *__restrict__ dstv,
     constexpr size_t TILE = (size_t)U * 32;  // vectors per warp per iteration
     const size_t ntiles = (nvec + TILE - 1) / TILE;
 
+    pdl_launch_dependents();
+    pdl_wait();
     if (blockIdx.x == 0) copy_edges(e, threadIdx.x);
 
     for (size_t t = gwarp; t < ntiles; t += warps_total) {
@@ -161,6 +163,8 @@ __device__ __forceinline__ void st_v8(void *p, const V8 &v) {
 template <int U>
 __global__ void __launch_bounds__(512) copy_vec32_kernel(uint8_t *__restrict__ dst, const uint8_t *__restrict__ src,
                                                          size_t n32, Edges e) {
+    pdl_launch_dependents();
+    pdl_wait();
     if (blockIdx.x == 0) copy_edges(e, threadIdx.x);
     const int lane = threadIdx.x & 31;
     const size_t warps_total = (size_t)gridDim.x * (blockDim.x >> 5);
@@ -201,6 +205,12 @@ __global__ void __launch_bounds__(32) copy_tma_kernel(uint8_t *__restrict__ dst,
     static_assert(L >= 1 && L < S, "need at least one stage of slack between loads and stores");
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)S * chunk);
 
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {  // barrier set-up overlaps the previous kernel's tail
+        for (int s = 0; s < S; ++s) mbar_init(smem_addr(bars) + 8 * s, 1);
+        mbar_init_fence();
+    }
+    pdl_wait();
     if (blockIdx.x == 0 && threadIdx.x != 0) {
         // lanes 1..15 -> head bytes, lanes 16..31 -> tail bytes
         const int t = threadIdx.x;
@@ -219,8 +229,6 @@ __global__ void __launch_bounds__(32) copy_tma_kernel(uint8_t *__restrict__ dst,
 
     const uint32_t smem_base = smem_addr(smem);
     const uint32_t bar_base = smem_addr(bars);
-    for (int s = 0; s < S; ++s) mbar_init(bar_base + 8 * s, 1);
-    mbar_init_fence();
 
     uint64_t pol = 0;
     if (HINT) pol = policy_evict_first();
@@ -275,6 +283,8 @@ struct PeerPtrs {
 template <int U, int MODE>
 __global__ void __launch_bounds__(512) alltoall_push_kernel(PeerPtrs peers, const uint4 *__restrict__ send,
                                                             size_t chunk_vec, int n, int rank) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int slot = blockIdx.x % n;
     const int peer = (rank + 1 + slot) % n;
@@ -336,12 +346,12 @@ Split split_copy(void *dst, const void *src, size_t bytes) {
 template <int SW, int U>
 int launch_vec_mode(int mode, int grid, int threads, cudaStream_t st, uint4 *dstv, const uint4 *srcv, size_t nvec,
                     int sb8, const Edges &e) {
+    const size_t pad = (size_t)tuning().copy_vec_smem_pad;
     switch (mode) {
-        case 1: copy_vec_kernel<SW, U, 1><<<grid, threads, 0, st>>>(dstv, srcv, nvec, sb8, e); break;
-        case 2: copy_vec_kernel<SW, U, 2><<<grid, threads, 0, st>>>(dstv, srcv, nvec, sb8, e); break;
-        default: copy_vec_kernel<SW, U, 0><<<grid, threads, 0, st>>>(dstv, srcv, nvec, sb8, e); break;
+        case 1: return launch_kernel(copy_vec_kernel<SW, U, 1>, grid, threads, pad, st, dstv, srcv, nvec, sb8, e);
+        case 2: return launch_kernel(copy_vec_kernel<SW, U, 2>, grid, threads, pad, st, dstv, srcv, nvec, sb8, e);
+        default: return launch_kernel(copy_vec_kernel<SW, U, 0>, grid, threads, pad, st, dstv, srcv, nvec, sb8, e);
     }
-    return check_launch();
 }
 
 template <int SW>
@@ -406,25 +416,16 @@ int launch_vec32(void *dst, const void *src, size_t bytes, int ctas, cudaStream_
     if (need == 0) need = 1;
     size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * tu.copy_vec_ctas_sm * (512 / threads);
     const int grid = (int)(need < cap ? need : cap);
-    if (unroll == 4) copy_vec32_kernel<4><<<grid, threads, 0, st>>>(d + head, s + head, n32, e);
-    else copy_vec32_kernel<2><<<grid, threads, 0, st>>>(d + head, s + head, n32, e);
-    return check_launch();
+    if (unroll == 4) return launch_kernel(copy_vec32_kernel<4>, grid, threads, 0, st, d + head, s + head, n32, e);
+    return launch_kernel(copy_vec32_kernel<2>, grid, threads, 0, st, d + head, s + head, n32, e);
 }
 
 template <int S, int L>
 int launch_tma_cfg(bool hint, int grid, size_t smem, cudaStream_t st, uint8_t *d, const uint8_t *s, size_t body,
                    uint32_t chunk, const Edges &e) {
-    cudaError_t err;
-    if (hint) {
-        err = cudaFuncSetAttribute(copy_tma_kernel<S, L, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (err != cudaSuccess) return (int)err;
-        copy_tma_kernel<S, L, true><<<grid, 32, smem, st>>>(d, s, body, chunk, e);
-    } else {
-        err = cudaFuncSetAttribute(copy_tma_kernel<S, L, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (err != cudaSuccess) return (int)err;
-        copy_tma_kernel<S, L, false><<<grid, 32, smem, st>>>(d, s, body, chunk, e);
-    }
-    return check_launch();
+    const size_t total = smem + (size_t)tuning().tma_smem_pad;
+    if (hint) return launch_kernel(copy_tma_kernel<S, L, true>, grid, 32, total, st, d, s, body, chunk, e);
+    return launch_kernel(copy_tma_kernel<S, L, false>, grid, 32, total, st, d, s, body, chunk, e);
 }
 
 int launch_tma(const Split &sp, int ctas, cudaStream_t st) {
@@ -510,9 +511,8 @@ extern "C" int lcb_alltoall_push(void *const *peer_recv, const void *send, size_
     if (per_peer > cap) per_peer = cap;
     if (per_peer == 0) per_peer = 1;
     const int grid = (int)(per_peer * n_ranks);
-    alltoall_push_kernel<4, 0><<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-        pp, static_cast<const uint4 *>(send), chunk_vec, n_ranks, rank);
-    return check_launch();
+    return launch_kernel(alltoall_push_kernel<4, 0>, grid, threads, 0, static_cast<cudaStream_t>(stream), pp,
+                         static_cast<const uint4 *>(send), chunk_vec, n_ranks, rank);
 }
 
 extern "C" int lcb_device_error_word(unsigned int *out) {

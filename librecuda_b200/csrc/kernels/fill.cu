@@ -32,6 +32,8 @@ __device__ __forceinline__ void fill_edges(const FillEdges &e, int t) {
 
 template <int U>
 __global__ void __launch_bounds__(512) memset_vec_kernel(uint4 *__restrict__ dstv, size_t nvec, FillEdges e) {
+    pdl_launch_dependents();
+    pdl_wait();
     if (blockIdx.x == 0) fill_edges(e, threadIdx.x);
     const uint4 p = make_uint4(e.pattern, e.pattern, e.pattern, e.pattern);
     const size_t tile = (size_t)U * blockDim.x;
@@ -58,15 +60,20 @@ template <bool HINT>
 __global__ void __launch_bounds__(256) memset_bulk_kernel(uint8_t *__restrict__ body_dst, size_t body, uint32_t chunk,
                                                           FillEdges e) {
     extern __shared__ __align__(128) uint8_t smem[];
-    if (blockIdx.x == 0) fill_edges(e, threadIdx.x);
+    pdl_launch_dependents();
     const size_t nchunks = (body + chunk - 1) / chunk;
     const size_t issuers = blockDim.x >> 5;
-    if ((size_t)blockIdx.x * issuers >= nchunks) return;
-    const uint4 p = make_uint4(e.pattern, e.pattern, e.pattern, e.pattern);
-    uint4 *tile = reinterpret_cast<uint4 *>(smem);
-    for (uint32_t i = threadIdx.x; i < chunk / 16; i += blockDim.x) tile[i] = p;
-    fence_generic_to_async_smem();
+    const bool has_chunks = (size_t)blockIdx.x * issuers < nchunks;
+    if (has_chunks) {  // the tile is built while the previous kernel on the stream is still draining
+        const uint4 p = make_uint4(e.pattern, e.pattern, e.pattern, e.pattern);
+        uint4 *tile = reinterpret_cast<uint4 *>(smem);
+        for (uint32_t i = threadIdx.x; i < chunk / 16; i += blockDim.x) tile[i] = p;
+        fence_generic_to_async_smem();
+    }
     __syncthreads();
+    pdl_wait();
+    if (blockIdx.x == 0) fill_edges(e, threadIdx.x);
+    if (!has_chunks) return;
     if ((threadIdx.x & 31) != 0) return;
     uint64_t pol = 0;
     if (HINT) pol = policy_evict_first();
@@ -86,6 +93,8 @@ __global__ void __launch_bounds__(512) index_fill_kernel(float *__restrict__ dst
                                                          size_t nvec) {
     // head elements (until dst+head is 16-byte aligned) and tail elements go out as scalars
     float4 *dst4 = reinterpret_cast<float4 *>(dst + head);
+    pdl_launch_dependents();
+    pdl_wait();
     if (blockIdx.x == 0) {
         const int t = threadIdx.x;
         if (t < head) dst[t] = (float)t;
@@ -109,6 +118,8 @@ __global__ void __launch_bounds__(512) index_fill_kernel(float *__restrict__ dst
 template <bool VEC>
 __global__ void __launch_bounds__(512) axpb_kernel(float *__restrict__ y, const float *__restrict__ x, float a, float b,
                                                    size_t count) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (VEC) {
@@ -193,17 +204,8 @@ int memset_any(void *dst, uint32_t pattern, int elem, size_t count, int path, in
         const size_t need = (nchunks + issuers - 1) / issuers;
         size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * tu.memset_bulk_ctas_sm;
         const int grid = (int)(need < cap ? (need ? need : 1) : cap);
-        cudaError_t err;
-        if (tu.memset_cache_hint) {
-            err = cudaFuncSetAttribute(memset_bulk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)chunk);
-            if (err != cudaSuccess) return (int)err;
-            memset_bulk_kernel<true><<<grid, bthreads, chunk, st>>>(body, nvec * 16, chunk, e);
-        } else {
-            err = cudaFuncSetAttribute(memset_bulk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)chunk);
-            if (err != cudaSuccess) return (int)err;
-            memset_bulk_kernel<false><<<grid, bthreads, chunk, st>>>(body, nvec * 16, chunk, e);
-        }
-        return check_launch();
+        if (tu.memset_cache_hint) return launch_kernel(memset_bulk_kernel<true>, grid, bthreads, chunk, st, body, nvec * 16, chunk, e);
+        return launch_kernel(memset_bulk_kernel<false>, grid, bthreads, chunk, st, body, nvec * 16, chunk, e);
     }
     if (path != 1) return 1;
     int threads = tu.memset_threads;
@@ -217,13 +219,13 @@ int memset_any(void *dst, uint32_t pattern, int elem, size_t count, int path, in
     size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * tu.memset_ctas_sm * (512 / threads);
     const int grid = (int)(need < cap ? need : cap);
     uint4 *dv = reinterpret_cast<uint4 *>(body);
+    const size_t pad = (size_t)tu.memset_smem_pad;
     switch (unroll) {
-        case 1: memset_vec_kernel<1><<<grid, threads, 0, st>>>(dv, nvec, e); break;
-        case 2: memset_vec_kernel<2><<<grid, threads, 0, st>>>(dv, nvec, e); break;
-        case 4: memset_vec_kernel<4><<<grid, threads, 0, st>>>(dv, nvec, e); break;
-        default: memset_vec_kernel<8><<<grid, threads, 0, st>>>(dv, nvec, e); break;
+        case 1: return launch_kernel(memset_vec_kernel<1>, grid, threads, pad, st, dv, nvec, e);
+        case 2: return launch_kernel(memset_vec_kernel<2>, grid, threads, pad, st, dv, nvec, e);
+        case 4: return launch_kernel(memset_vec_kernel<4>, grid, threads, pad, st, dv, nvec, e);
+        default: return launch_kernel(memset_vec_kernel<8>, grid, threads, pad, st, dv, nvec, e);
     }
-    return check_launch();
 }
 
 }  // namespace
@@ -260,9 +262,8 @@ extern "C" int lcb_index_fill_f32(float *dst, size_t count, lcbStream stream) {
     if (head > count) head = count;
     const size_t nvec = (count - head) / 4;
     const int threads = 512;
-    const int grid = grid_for(nvec, threads, 4);
-    index_fill_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(dst, count, (int)head, nvec);
-    return check_launch();
+    const int grid = grid_for(nvec, threads, tuning().fill_ctas_sm);
+    return launch_kernel(index_fill_kernel, grid, threads, 0, static_cast<cudaStream_t>(stream), dst, count, (int)head, nvec);
 }
 
 extern "C" int lcb_axpb_f32(float *y, const float *x, float a, float b, size_t count, lcbStream stream) {
@@ -273,12 +274,8 @@ extern "C" int lcb_axpb_f32(float *y, const float *x, float a, float b, size_t c
     const bool vec = ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(x)) & 15) == 0;
     const int threads = 512;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (vec) {
-        axpb_kernel<true><<<grid_for(count / 4 + 1, threads, 4), threads, 0, st>>>(y, x, a, b, count);
-    } else {
-        axpb_kernel<false><<<grid_for(count, threads, 4), threads, 0, st>>>(y, x, a, b, count);
-    }
-    return check_launch();
+    if (vec) return launch_kernel(axpb_kernel<true>, grid_for(count / 4 + 1, threads, tuning().fill_ctas_sm), threads, 0, st, y, x, a, b, count);
+    return launch_kernel(axpb_kernel<false>, grid_for(count, threads, 4), threads, 0, st, y, x, a, b, count);
 }
 
 extern "C" int lcb_fill_splitmix64(void *dst, size_t bytes, uint64_t seed, lcbStream stream) {

@@ -21,11 +21,16 @@ static const Tuning kDefaults = {
         /*memset_path*/ 0,
         /*memset_unroll*/ 8,
         /*memset_threads*/ 256,
-        /*memset_ctas_sm*/ 4,
+        /*memset_ctas_sm*/ 64,
         /*memset_chunk*/ 32768,
         /*memset_issuers*/ 4,
         /*memset_bulk_ctas_sm*/ 2,
         /*memset_cache_hint*/ 0,
+        /*pdl*/ 1,
+        /*copy_vec_smem_pad*/ 0,
+        /*tma_smem_pad*/ 0,
+        /*memset_smem_pad*/ 0,
+        /*fill_ctas_sm*/ 64,
 };
 
 Tuning &tuning() {
@@ -79,6 +84,11 @@ extern "C" int lcb_tune(const char *name, int value) {
     LCB_KNOB(memset_issuers)
     LCB_KNOB(memset_bulk_ctas_sm)
     LCB_KNOB(memset_cache_hint)
+    LCB_KNOB(pdl)
+    LCB_KNOB(copy_vec_smem_pad)
+    LCB_KNOB(tma_smem_pad)
+    LCB_KNOB(memset_smem_pad)
+    LCB_KNOB(fill_ctas_sm)
 #undef LCB_KNOB
     return 1;
 }
@@ -132,4 +142,13 @@ extern "C" int lcb_timer_destroy(void *timer) {
 
 extern "C" int lcb_stream_synchronize(lcbStream stream) {
     return (int)cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+}
+
+// ---- vendor paths, for side-by-side measurement only (never used by the library's own data path) ---------
+extern "C" int lcb_vendor_memcpy_d2d(void *dst, const void *src, size_t bytes, lcbStream stream) {
+    return (int)cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int lcb_vendor_memset_d8(void *dst, unsigned char value, size_t bytes, lcbStream stream) {
+    return (int)cudaMemsetAsync(dst, value, bytes, static_cast<cudaStream_t>(stream));
 }
