@@ -406,8 +406,10 @@ def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_r
     stream.run()
     from librecuda_b200 import multirank as mr
 
-    peers = mr.open_peers(dist, recv)
+    peers = mr.open_peers(dist, recv)          # every rank's receive buffer (targets of remote stores)
+    send_peers = mr.open_peers(dist, send)     # every rank's send buffer (sources of remote loads)
     peer_arr = (C.c_void_p * G)(*peers)
+    send_arr = (C.c_void_p * G)(*send_peers)
     out = {"world": G, "nominal_GBps": NVLINK_NOMINAL, "measured_peer_copy_GBps": NVLINK_MEASURED}
 
     def report(name, bytes_per_gpu, ms):
@@ -416,29 +418,26 @@ def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_r
                      "frac_of_nominal_900": round(gbps / NVLINK_NOMINAL, 4),
                      "frac_of_measured_770": round(gbps / NVLINK_MEASURED, 4)}
 
-    # 1. partitioned peer push: every rank stores its shard into the next rank's buffer (all ports busy)
-    nxt = peers[(rank + 1) % G]
+    def measure(name, fn, bytes_per_gpu):
+        for _ in range(3):
+            fn()
+        barrier()
+        ms = max_over_ranks(timed_loop(api, stream, fn, steps))
+        barrier()
+        report(name, bytes_per_gpu, ms)
 
-    def push():
-        api.lcb_check(lib.lcb_copy_d2d(nxt, send.ptr, shard, native), "peer push")
+    # 1. partitioned peer copy, every port busy: rank r moves a 1 GiB shard from / to its neighbour.
+    #    pull = the destination GPU loads from the source GPU (faster direction), push = the source GPU stores.
+    prev_send = send_peers[(rank - 1) % G]
+    nxt_recv = peers[(rank + 1) % G]
+    measure("p2p_shift_pull_1GiB", lambda: api.lcb_check(lib.lcb_copy_d2d(recv.ptr, prev_send, shard, native), "peer pull"), shard)
+    measure("p2p_shift_push_1GiB", lambda: api.lcb_check(lib.lcb_copy_d2d(nxt_recv, send.ptr, shard, native), "peer push"), shard)
 
-    for _ in range(3):
-        push()
-    barrier()
-    ms = max_over_ranks(timed_loop(api, stream, push, steps))
-    barrier()
-    report("p2p_shift_push_1GiB", shard, ms)
-
-    # 2. all-to-all, own kernel: one launch stores every chunk into its peer slot
-    def a2a():
-        api.lcb_check(lib.lcb_alltoall_push(peer_arr, send.ptr, chunk, G, rank, native), "alltoall push")
-
-    for _ in range(3):
-        a2a()
-    barrier()
-    ms = max_over_ranks(timed_loop(api, stream, a2a, steps))
-    barrier()
-    report("alltoall_own_push", (G - 1) * chunk, ms)
+    # 2. all-to-all, own kernels: one launch per rank moves every chunk (pull = remote loads, push = remote stores)
+    measure("alltoall_own_push", lambda: api.lcb_check(lib.lcb_alltoall_push(peer_arr, send.ptr, chunk, G, rank, native), "a2a push"), (G - 1) * chunk)
+    stream.memset_d8(recv, 0, G * chunk)
+    stream.run()
+    measure("alltoall_own_pull", lambda: api.lcb_check(lib.lcb_alltoall_pull(send_arr, recv.ptr, chunk, G, rank, native), "a2a pull"), (G - 1) * chunk)
     # verify: slot r of my recv buffer must be chunk `rank` of rank r's send buffer
     ok = True
     resb = api.DeviceBuffer(16)
@@ -452,7 +451,7 @@ def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_r
         stream.run()
         ok = ok and int(got[0]) == 0
         full.free()
-    out["alltoall_own_push"]["verified"] = ok
+    out["alltoall_own_pull"]["verified"] = ok
 
     # 3. all-to-all and broadcast through NCCL (torch.distributed): the named library path
     ts = torch.empty(G * chunk, dtype=torch.uint8, device="cuda")
@@ -487,6 +486,7 @@ def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_r
     del tb
     barrier()
     mr.close_peers(dist, peers)
+    mr.close_peers(dist, send_peers)
     barrier()
     for b in (send, recv, resb):
         b.free()

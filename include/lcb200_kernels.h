@@ -65,6 +65,13 @@ int lcb_axpb_f32(float *y, const float *x, float a, float b, size_t count, lcbSt
  * device pointers (n_ranks <= 16).  ref: none (the reference is single-GPU, librecuda.cpp:61). */
 int lcb_alltoall_push(void *const *peer_recv, const void *send, size_t chunk_bytes, int n_ranks, int rank,
                       lcbStream stream);
+/* The same exchange by remote LOADS: for every j, chunk `rank` of peer_send[j] (peer j's send buffer) is
+ * copied to recv + j * chunk_bytes.  peer_send is a HOST array of n_ranks device pointers.  On NVLink 5
+ * remote loads win when the links are busy in one direction only (786 vs 716 GB/s per GPU measured); when all
+ * ranks exchange at once the push form is faster (704 vs 665).  The caller makes sure every peer's send buffer
+ * is ready before the launch and stays untouched until all ranks are done. */
+int lcb_alltoall_pull(void *const *peer_send, void *recv, size_t chunk_bytes, int n_ranks, int rank,
+                      lcbStream stream);
 
 /* ---- verification helpers that run on the device (used by tests and the benchmark) ------------- */
 

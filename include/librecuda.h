@@ -206,9 +206,13 @@ LIBRECUDA_EXPORT libreCudaStatus_t libreCuMemcpyPartitioned(void *const *dsts, c
 // One rank's half of an all-to-all over peer-mapped buffers: chunk j of `sendBuf` is stored into
 // peerRecvBufs[j] + rank * chunkBytes, for every j in [0, nRanks), by one kernel on `stream`.
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAllPush(void *const *peerRecvBufs, const void *sendBuf, size_t chunkBytes, int nRanks, int rank, LibreCUstream stream);
+// The same exchange by remote loads: chunk `rank` of peerSendBufs[j] is
+// loaded into recvBuf + j * chunkBytes, for every j, by one kernel on `stream`.  Peers' send buffers must be
+// complete before this runs and unchanged until every rank has finished.
+LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAllPull(void *const *peerSendBufs, void *recvBuf, size_t chunkBytes, int nRanks, int rank, LibreCUstream stream);
 // Single-process collectives over the devices of `streams[0..nDev)` (one stream per device, peer
 // access enabled).  useNccl != 0 runs them through NCCL (ncclSend/ncclRecv, ncclBroadcast);
-// useNccl == 0 runs the library's own peer-store kernels.
+// useNccl == 0 runs the library's own peer-memory kernels.
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, size_t chunkBytes, int nDev, const LibreCUstream *streams, int useNccl);
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount, int nDev, const LibreCUstream *streams, int useNccl);
 

@@ -33,6 +33,7 @@ LCB_FUNCTIONS = {
     "lcb_index_fill_f32": (i32, [vp, sz, vp]),
     "lcb_axpb_f32": (i32, [vp, vp, C.c_float, C.c_float, sz, vp]),
     "lcb_alltoall_push": (i32, [vpp, vp, sz, i32, i32, vp]),
+    "lcb_alltoall_pull": (i32, [vpp, vp, sz, i32, i32, vp]),
     "lcb_fill_splitmix64": (i32, [vp, sz, u64, vp]),
     "lcb_compare_bytes": (i32, [vp, vp, sz, vp, vp]),
     "lcb_checksum64": (i32, [vp, sz, vp, vp, vp]),
@@ -108,6 +109,7 @@ LIBRECU_FUNCTIONS = {
     "libreCuPartitionPlan": (i32, [sz, i32, sz, C.POINTER(sz)]),
     "libreCuMemcpyPartitioned": (i32, [vpp, vp, sz, i32, sz, vpp]),
     "libreCuAllToAllPush": (i32, [vpp, vp, sz, i32, i32, vp]),
+    "libreCuAllToAllPull": (i32, [vpp, vp, sz, i32, i32, vp]),
     "libreCuAllToAll": (i32, [vpp, vpp, sz, i32, vpp, i32]),
     "libreCuBroadcast": (i32, [vpp, i32, sz, i32, vpp, i32]),
     "libreCuIpcGetMemHandle": (i32, [vp, vp]),

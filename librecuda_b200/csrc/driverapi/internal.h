@@ -149,7 +149,7 @@ struct LibreCUEvent_ {
 namespace lcu {
 
 struct Command {
-    enum Kind { CopyKernel, CopyEngine, Memset, Launch, EventRecord, WaitEvent, AllToAllPush };
+    enum Kind { CopyKernel, CopyEngine, Memset, Launch, EventRecord, WaitEvent, AllToAllPush, AllToAllPull };
     Kind kind;
     bool async = false;
     // copies / memset

@@ -2,8 +2,10 @@
 // movement over NVLink, and inter-process buffer sharing.  The reference is single-GPU (one process-global
 // context, driverapi/src/librecuda.cpp:61), so everything here is additive.
 //
-// Own-kernel paths store straight into peer memory with the library's copy kernels (plain vector stores or
-// non-multicast bulk copies); NCCL is used only for the broadcast and all-to-all collectives and is loaded
+// Own-kernel paths read straight from (or write straight into) peer memory with the library's copy kernels
+// (plain vector accesses or non-multicast bulk copies).  Measured on NVLink 5: when only one direction of a
+// link carries data (scatter from a root) remote LOADS are faster (786 vs 716 GB/s per GPU); when both
+// directions are busy (all-to-all, ring shift) remote STORES are (704 vs 665).  NCCL is used only for the broadcast and all-to-all collectives and is loaded
 // lazily with dlopen so that programs that never call them do not need it.
 #include <dlfcn.h>
 #include <nccl.h>
@@ -79,24 +81,35 @@ libreCudaStatus_t libreCuMemcpyPartitioned(void *const *dsts, const void *src, s
 
 // ---- all-to-all ---------------------------------------------------------------------------------------------
 
-libreCudaStatus_t libreCuAllToAllPush(void *const *peerRecvBufs, const void *sendBuf, size_t chunkBytes, int nRanks,
-                                      int rank, LibreCUstream stream) {
-    LIBRECUDA_VALIDATE(peerRecvBufs != nullptr && sendBuf != nullptr && stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+static libreCudaStatus_t record_alltoall(bool pull, void *const *peerBufs, void *mine, size_t chunkBytes, int nRanks,
+                                         int rank, LibreCUstream stream) {
+    LIBRECUDA_VALIDATE(peerBufs != nullptr && mine != nullptr && stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
     LIBRECUDA_VALIDATE(nRanks >= 1 && nRanks <= 16 && rank >= 0 && rank < nRanks, LIBRECUDA_ERROR_INVALID_VALUE);
     LIBRECUDA_VALIDATE((chunkBytes & 15) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
-    LIBRECUDA_VALIDATE((reinterpret_cast<uintptr_t>(sendBuf) & 15) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
+    LIBRECUDA_VALIDATE((reinterpret_cast<uintptr_t>(mine) & 15) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
     for (int j = 0; j < nRanks; ++j) {
-        LIBRECUDA_VALIDATE(peerRecvBufs[j] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-        LIBRECUDA_VALIDATE((reinterpret_cast<uintptr_t>(peerRecvBufs[j]) & 15) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(peerBufs[j] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE((reinterpret_cast<uintptr_t>(peerBufs[j]) & 15) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
     }
     if (chunkBytes == 0) LIBRECUDA_SUCCEED();
     Command c;
-    c.kind = Command::AllToAllPush;
-    c.src = sendBuf;
+    c.kind = pull ? Command::AllToAllPull : Command::AllToAllPush;
+    c.src = pull ? nullptr : mine;
+    c.dst = pull ? mine : nullptr;
     c.bytes = chunkBytes;
     c.rank = rank;
-    c.peers.assign(peerRecvBufs, peerRecvBufs + nRanks);
+    c.peers.assign(peerBufs, peerBufs + nRanks);
     return record(stream, std::move(c));
+}
+
+libreCudaStatus_t libreCuAllToAllPush(void *const *peerRecvBufs, const void *sendBuf, size_t chunkBytes, int nRanks,
+                                      int rank, LibreCUstream stream) {
+    return record_alltoall(false, peerRecvBufs, const_cast<void *>(sendBuf), chunkBytes, nRanks, rank, stream);
+}
+
+libreCudaStatus_t libreCuAllToAllPull(void *const *peerSendBufs, void *recvBuf, size_t chunkBytes, int nRanks, int rank,
+                                      LibreCUstream stream) {
+    return record_alltoall(true, peerSendBufs, recvBuf, chunkBytes, nRanks, rank, stream);
 }
 
 // ---- NCCL, loaded on first use ------------------------------------------------------------------------------
@@ -228,8 +241,9 @@ libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, 
         LCU_NCCL(n, n->GroupEnd());
     } else {
         LIBRECUDA_VALIDATE((chunkBytes & 15) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
-        // rank r must not overwrite a receive slot its peer is still sending from / reading: start after
-        // everything submitted so far on every stream
+        // rank r must not overwrite a receive slot its peer may still be using: start after everything
+        // submitted so far on every stream.  Stores, not loads: with every link busy in both directions remote
+        // stores are the faster form (704 vs 665 GB/s per GPU measured).
         LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
         for (int r = 0; r < nDev; ++r) {
             LIBRECUDA_ERR_PROPAGATE(bind(streams[r]->ctx));
@@ -259,37 +273,37 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
         LCU_NCCL(n, n->GroupEnd());
         return rebind_current();
     }
-    // Own path, two phases over peer stores.  Phase 1: the root scatters shard g to device g (each byte
-    // leaves the root once).  Phase 2: every non-root device forwards its shard to the other non-root
-    // devices, so the remaining traffic is spread over all NVLink ports instead of the root's alone.
+    // Own path, two phases of remote loads (the faster direction while the root only sends).  The buffer is cut into one shard
+    // per non-root device.  Phase 1: device g pulls shard g from the root (every byte leaves the root once).
+    // Phase 2: every non-root device pulls the other shards from the devices that own them, so that traffic
+    // is spread over all NVLink ports instead of the root's alone.
+    std::vector<int> owners;
+    for (int g = 0; g < nDev; ++g)
+        if (g != root) owners.push_back(g);
+    const int parts = (int)owners.size();
     size_t off[17];
-    LIBRECUDA_ERR_PROPAGATE(libreCuPartitionPlan(byteCount, nDev, 0, off));
+    LIBRECUDA_ERR_PROPAGATE(libreCuPartitionPlan(byteCount, parts, 0, off));
     LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
-    LIBRECUDA_ERR_PROPAGATE(bind(streams[root]->ctx));
     const uint8_t *src = static_cast<const uint8_t *>(bufs[root]);
-    std::vector<cudaEvent_t> landed(nDev, nullptr);
-    for (int g = 0; g < nDev; ++g) {
-        if (g == root || off[g + 1] == off[g]) continue;
-        LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[g]) + off[g], src + off[g], off[g + 1] - off[g], streams[root]->main));
-        LCU_CUDA(cudaEventCreateWithFlags(&landed[g], cudaEventDisableTiming));
-        LCU_CUDA(cudaEventRecord(landed[g], streams[root]->main));
-    }
-    // the root's own shard goes to everyone from the root
-    if (off[root + 1] > off[root]) {
-        for (int g = 0; g < nDev; ++g) {
-            if (g == root) continue;
-            LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[g]) + off[root], src + off[root], off[root + 1] - off[root],
-                                 streams[root]->main));
-        }
-    }
-    for (int g = 0; g < nDev; ++g) {
-        if (g == root || landed[g] == nullptr) continue;
+    std::vector<cudaEvent_t> landed(parts, nullptr);
+    for (int k = 0; k < parts; ++k) {
+        const int g = owners[k];
+        if (off[k + 1] == off[k]) continue;
         LIBRECUDA_ERR_PROPAGATE(bind(streams[g]->ctx));
-        LCU_CUDA(cudaStreamWaitEvent(streams[g]->main, landed[g], 0));
-        const uint8_t *mine = static_cast<const uint8_t *>(bufs[g]) + off[g];
-        for (int q = 0; q < nDev; ++q) {
-            if (q == root || q == g) continue;
-            LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[q]) + off[g], mine, off[g + 1] - off[g], streams[g]->main));
+        LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[g]) + off[k], src + off[k], off[k + 1] - off[k], streams[g]->main));
+        LCU_CUDA(cudaEventCreateWithFlags(&landed[k], cudaEventDisableTiming));
+        LCU_CUDA(cudaEventRecord(landed[k], streams[g]->main));
+    }
+    for (int kq = 0; kq < parts; ++kq) {
+        const int q = owners[kq];
+        LIBRECUDA_ERR_PROPAGATE(bind(streams[q]->ctx));
+        for (int step = 1; step < parts; ++step) {  // rotate the order so the pulls spread over the owners
+            const int k = (kq + step) % parts;
+            if (landed[k] == nullptr) continue;
+            const int g = owners[k];
+            LCU_CUDA(cudaStreamWaitEvent(streams[q]->main, landed[k], 0));
+            LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[q]) + off[k], static_cast<const uint8_t *>(bufs[g]) + off[k],
+                                 off[k + 1] - off[k], streams[q]->main));
         }
     }
     for (cudaEvent_t e : landed)

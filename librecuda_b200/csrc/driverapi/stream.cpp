@@ -102,6 +102,10 @@ static libreCudaStatus_t submit(LibreCUstream st, Command &c) {
             LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
             LCU_LCB(lcb_alltoall_push(c.peers.data(), c.src, c.bytes, (int)c.peers.size(), c.rank, lane));
             break;
+        case Command::AllToAllPull:
+            LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
+            LCU_LCB(lcb_alltoall_pull(c.peers.data(), c.dst, c.bytes, (int)c.peers.size(), c.rank, lane));
+            break;
         case Command::Launch: {
             LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
             LibreCUFunction f = c.fn;

@@ -37,6 +37,7 @@ struct Tuning {
     int tma_smem_pad;        // same for the bulk ring
     int memset_smem_pad;     // same for the vector memset
     int fill_ctas_sm;        // CTAs per SM worth of grid for index fill / axpb
+    int a2a_ctas_sm;         // CTAs per SM (all peers together) of the all-to-all push kernel
 };
 Tuning &tuning();
 

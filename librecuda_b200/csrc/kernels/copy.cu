@@ -16,8 +16,8 @@
 //                       (cp.async.bulk global->shared with mbarrier complete_tx, then shared->global in
 //                       bulk groups).  Non-multicast forms only, so the same kernel is usable with a peer
 //                       GPU's memory on either side.
-//  * alltoall_push_kernel  one launch that stores every chunk of a send buffer into the matching slot of
-//                       every peer's receive buffer (the copy fused with the exchange).
+//  * alltoall_kernel     one launch that moves every chunk of an all-to-all between this GPU and all its
+//                       peers (the copy fused with the exchange), by remote loads (pull) or stores (push).
 #include "common.cuh"
 #include "lcb200_kernels.h"
 
@@ -272,17 +272,24 @@ __global__ void __launch_bounds__(32) copy_tma_kernel(uint8_t *__restrict__ dst,
 }
 
 // ---------------------------------------------------------------------------------------------
-// all-to-all push
+// all-to-all (push and pull)
 // ---------------------------------------------------------------------------------------------
 struct PeerPtrs {
-    uint4 *recv[16];
+    uint4 *buf[16];
 };
 
-// CTA b serves peer (rank + 1 + b % n) % n, so consecutive CTAs feed different NVLink destinations and
-// every link is busy from the first wave on; within a peer the CTAs stride over warp tiles.
-template <int U, int MODE>
-__global__ void __launch_bounds__(512) alltoall_push_kernel(PeerPtrs peers, const uint4 *__restrict__ send,
-                                                            size_t chunk_vec, int n, int rank) {
+// The exchange fused into one copy kernel.  CTA b serves peer (rank + 1 + b % n) % n, so consecutive CTAs
+// talk to different GPUs and every NVLink port is busy from the first wave on; within a peer the CTAs stride
+// over warp tiles.
+//   PULL = false: `mine` is this rank's send buffer, peers.buf[j] the receive buffers: chunk j of `mine` is
+//                 STORED to peers.buf[j] + rank * chunk.
+//   PULL = true:  `mine` is this rank's receive buffer, peers.buf[j] the send buffers: chunk `rank` of
+//                 peers.buf[j] is LOADED into mine + j * chunk.
+// Measured on NVLink 5 (GB/s per GPU): one direction of a link busy -- loads 786, stores 716; both directions
+// busy, as in a real all-to-all -- stores 704, loads 665 (load requests compete with the peer's data).
+template <int U, int MODE, bool PULL>
+__global__ void __launch_bounds__(512) alltoall_kernel(PeerPtrs peers, uint4 *__restrict__ mine,
+                                                       size_t chunk_vec, int n, int rank) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -294,8 +301,8 @@ __global__ void __launch_bounds__(512) alltoall_push_kernel(PeerPtrs peers, cons
     const size_t gwarp = cta_in_peer * (blockDim.x >> 5) + (threadIdx.x >> 5);
     constexpr size_t TILE = (size_t)U * 32;
     const size_t ntiles = (chunk_vec + TILE - 1) / TILE;
-    const uint4 *s = send + (size_t)peer * chunk_vec;
-    uint4 *d = peers.recv[peer] + (size_t)rank * chunk_vec;
+    const uint4 *s = PULL ? peers.buf[peer] + (size_t)rank * chunk_vec : mine + (size_t)peer * chunk_vec;
+    uint4 *d = PULL ? mine + (size_t)peer * chunk_vec : peers.buf[peer] + (size_t)rank * chunk_vec;
     for (size_t t = gwarp; t < ntiles; t += warps_total) {
         const size_t base = t * TILE;
         uint4 v[U];
@@ -491,28 +498,43 @@ extern "C" int lcb_copy_d2d(void *dst, const void *src, size_t bytes, lcbStream 
     return lcb_copy_d2d_ex(dst, src, bytes, LCB_COPY_AUTO, 0, stream);
 }
 
-extern "C" int lcb_alltoall_push(void *const *peer_recv, const void *send, size_t chunk_bytes, int n_ranks, int rank,
-                                 lcbStream stream) {
-    using namespace lcb;
-    if (n_ranks < 1 || n_ranks > 16 || rank < 0 || rank >= n_ranks || peer_recv == nullptr || send == nullptr) return 1;
+namespace lcb {
+namespace {
+int launch_alltoall(bool pull, void *const *peer_bufs, void *mine, size_t chunk_bytes, int n_ranks, int rank,
+                    lcbStream stream) {
+    if (n_ranks < 1 || n_ranks > 16 || rank < 0 || rank >= n_ranks || peer_bufs == nullptr || mine == nullptr) return 1;
     if (chunk_bytes == 0) return 0;
-    if ((chunk_bytes & 15) || (reinterpret_cast<uintptr_t>(send) & 15)) return 1;
+    if ((chunk_bytes & 15) || (reinterpret_cast<uintptr_t>(mine) & 15)) return 1;
     PeerPtrs pp{};
     for (int j = 0; j < n_ranks; ++j) {
-        if (peer_recv[j] == nullptr || (reinterpret_cast<uintptr_t>(peer_recv[j]) & 15)) return 1;
-        pp.recv[j] = static_cast<uint4 *>(peer_recv[j]);
+        if (peer_bufs[j] == nullptr || (reinterpret_cast<uintptr_t>(peer_bufs[j]) & 15)) return 1;
+        pp.buf[j] = static_cast<uint4 *>(peer_bufs[j]);
     }
     const Tuning &tu = tuning();
     const int threads = 512;
     const size_t chunk_vec = chunk_bytes / 16;
     const size_t per_cta = (size_t)4 * threads;
     size_t per_peer = (chunk_vec + per_cta - 1) / per_cta;
-    size_t cap = ((size_t)sm_count() * tu.copy_vec_ctas_sm + n_ranks - 1) / n_ranks;
+    size_t cap = ((size_t)sm_count() * tu.a2a_ctas_sm + n_ranks - 1) / n_ranks;
     if (per_peer > cap) per_peer = cap;
     if (per_peer == 0) per_peer = 1;
     const int grid = (int)(per_peer * n_ranks);
-    return launch_kernel(alltoall_push_kernel<4, 0>, grid, threads, 0, static_cast<cudaStream_t>(stream), pp,
-                         static_cast<const uint4 *>(send), chunk_vec, n_ranks, rank);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint4 *m = static_cast<uint4 *>(mine);
+    if (pull) return launch_kernel(alltoall_kernel<4, 2, true>, grid, threads, 0, st, pp, m, chunk_vec, n_ranks, rank);
+    return launch_kernel(alltoall_kernel<4, 2, false>, grid, threads, 0, st, pp, m, chunk_vec, n_ranks, rank);
+}
+}  // namespace
+}  // namespace lcb
+
+extern "C" int lcb_alltoall_push(void *const *peer_recv, const void *send, size_t chunk_bytes, int n_ranks, int rank,
+                                 lcbStream stream) {
+    return lcb::launch_alltoall(false, peer_recv, const_cast<void *>(send), chunk_bytes, n_ranks, rank, stream);
+}
+
+extern "C" int lcb_alltoall_pull(void *const *peer_send, void *recv, size_t chunk_bytes, int n_ranks, int rank,
+                                 lcbStream stream) {
+    return lcb::launch_alltoall(true, peer_send, recv, chunk_bytes, n_ranks, rank, stream);
 }
 
 extern "C" int lcb_device_error_word(unsigned int *out) {

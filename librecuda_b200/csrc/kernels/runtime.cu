@@ -31,6 +31,7 @@ static const Tuning kDefaults = {
         /*tma_smem_pad*/ 0,
         /*memset_smem_pad*/ 0,
         /*fill_ctas_sm*/ 64,
+        /*a2a_ctas_sm*/ 1,
 };
 
 Tuning &tuning() {
@@ -89,6 +90,7 @@ extern "C" int lcb_tune(const char *name, int value) {
     LCB_KNOB(tma_smem_pad)
     LCB_KNOB(memset_smem_pad)
     LCB_KNOB(fill_ctas_sm)
+    LCB_KNOB(a2a_ctas_sm)
 #undef LCB_KNOB
     return 1;
 }

@@ -101,6 +101,8 @@ def test_kernel_layer_rejects_bad_arguments_without_touching_a_gpu():
     peers = (C.c_void_p * 2)(4096, 8192)
     assert N.lib.lcb_alltoall_push(peers, 4096, 24, 2, 0, None) == 1   # chunk not a multiple of 16
     assert N.lib.lcb_alltoall_push(peers, 4096, 32, 2, 5, None) == 1   # rank out of range
+    assert N.lib.lcb_alltoall_pull(peers, 4096, 24, 2, 0, None) == 1
+    assert N.lib.lcb_alltoall_pull(peers, 4097, 32, 2, 0, None) == 1   # misaligned receive buffer
 
 
 @pytest.mark.parametrize("total,parts,align", [(8 << 30, 8, 0), (8 << 30, 4, 2 << 20), (10 * (1 << 20) + 5, 4, 2 << 20),

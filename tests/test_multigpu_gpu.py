@@ -147,8 +147,9 @@ def test_all_to_all(gpus, use_nccl):
     ctxs[0].set_current()
 
 
-def test_all_to_all_push_recorded_per_rank(gpus):
-    # the per-rank half is an ordinary recorded stream operation
+@pytest.mark.parametrize("pull", [False, True])
+def test_all_to_all_recorded_per_rank(gpus, pull):
+    # the per-rank half (push: remote stores, pull: remote loads) is an ordinary recorded stream operation
     ctxs, streams = gpus
     G = len(ctxs)
     chunk = MiB + 16
@@ -157,10 +158,18 @@ def test_all_to_all_push_recorded_per_rank(gpus):
     send = [_alloc_on(ctxs[g], G * chunk) for g in range(G)]
     recv = [_alloc_on(ctxs[g], G * chunk) for g in range(G)]
     rp = (C.c_void_p * G)(*[b.ptr for b in recv])
+    sp = (C.c_void_p * G)(*[b.ptr for b in send])
     for g in range(G):
         ctxs[g].set_current()
         streams[g].memcpy(send[g], send_h[g], G * chunk)
-        api.check(lib.libreCuAllToAllPush(rp, send[g].ptr, chunk, G, g, streams[g].handle))
+        if not pull:
+            api.check(lib.libreCuAllToAllPush(rp, send[g].ptr, chunk, G, g, streams[g].handle))
+    if pull:  # every send buffer must be complete before anyone loads from it
+        for s in streams:
+            s.run()
+        for g in range(G):
+            ctxs[g].set_current()
+            api.check(lib.libreCuAllToAllPull(sp, recv[g].ptr, chunk, G, g, streams[g].handle))
     for s in streams:
         s.commence()
     for s in streams:
@@ -168,6 +177,8 @@ def test_all_to_all_push_recorded_per_rank(gpus):
     for g in range(G):
         assert np.array_equal(_download(ctxs, streams, g, recv[g], G * chunk), want[g])
     assert lib.libreCuAllToAllPush(rp, send[0].ptr, 24, G, 0, streams[0].handle) == api.ERROR_INVALID_VALUE
+    assert lib.libreCuAllToAllPull(sp, recv[0].ptr, 24, G, 0, streams[0].handle) == api.ERROR_INVALID_VALUE
+    assert lib.libreCuAllToAllPull(sp, recv[0].ptr, 32, G, G, streams[0].handle) == api.ERROR_INVALID_VALUE
     for g in range(G):
         ctxs[g].set_current()
         send[g].free()
