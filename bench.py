@@ -397,7 +397,7 @@ def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_r
     lib = api.lib
     native = stream.native
     G = world
-    chunk = GiB if G <= 4 else GiB // 2  # all-to-all chunk per pair; (G-1) * chunk leaves every GPU
+    chunk = GiB  # all-to-all chunk per GPU pair; (G-1) * chunk leaves and enters every GPU
     shard = GiB
     send = api.DeviceBuffer(G * chunk)
     recv = api.DeviceBuffer(G * chunk)
@@ -453,10 +453,40 @@ def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_r
         full.free()
     out["alltoall_own_pull"]["verified"] = ok
 
-    # 3. all-to-all and broadcast through NCCL (torch.distributed): the named library path
+    # 3. partitioned copy of an 8 GiB buffer that lives on rank 0: shard g (2 MiB-aligned boundaries from
+    #    libreCuPartitionPlan) is pulled by rank g into its own memory; rank 0 keeps shard 0 with a local copy.
+    total = 8 * GiB
+    big = api.DeviceBuffer(total if rank == 0 else 4096)
+    if rank == 0:
+        api.lcb_check(lib.lcb_fill_splitmix64(big.ptr, total, 3, native), "fill")
+        stream.run()
+    big_peers = mr.open_peers(dist, big)
+    off, ln = mr.shard_of(total, G, rank)
+    mine = api.DeviceBuffer(max(ln, 16))
+    measure("partitioned_8GiB_from_rank0", lambda: api.lcb_check(lib.lcb_copy_d2d(mine.ptr, big_peers[0] + off, ln, native), "shard pull"),
+            total * (G - 1) // G)
+    out["partitioned_8GiB_from_rank0"]["note"] = "GB/s leaving rank 0 (its NVLink egress): (G-1)/G of 8 GiB / max-over-ranks time"
+    expect = api.DeviceBuffer(off + ln if off + ln > 0 else 16)   # seeded stream is keyed by position: regenerate the prefix
+    api.lcb_check(lib.lcb_fill_splitmix64(expect.ptr, off + ln, 3, native), "fill")
+    api.lcb_check(lib.lcb_compare_bytes(mine.ptr, expect.ptr + off, ln, resb.ptr, native), "cmp")
+    got = np.zeros(2, np.uint64)
+    stream.memcpy(got, resb, 16)
+    stream.run()
+    out["partitioned_8GiB_from_rank0"]["verified"] = int(got[0]) == 0
+    expect.free()
+    mine.free()
+    barrier()
+    mr.close_peers(dist, big_peers)
+    barrier()
+    big.free()
+
+    # 4. all-to-all and broadcast through NCCL (torch.distributed): the named library path.  Buffers are filled
+    #    and checked with this library's device-side generator / comparator.
     ts = torch.empty(G * chunk, dtype=torch.uint8, device="cuda")
-    tr = torch.empty(G * chunk, dtype=torch.uint8, device="cuda")
-    ts.random_(0, 256)
+    tr = torch.zeros(G * chunk, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    api.lcb_check(lib.lcb_fill_splitmix64(ts.data_ptr(), G * chunk, 100 + rank, native), "fill")
+    stream.run()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for _ in range(3):
         dist.all_to_all_single(tr, ts)
@@ -468,21 +498,36 @@ def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_r
     torch.cuda.synchronize()
     ms = max_over_ranks(ev0.elapsed_time(ev1) / steps)
     report("alltoall_nccl", (G - 1) * chunk, ms)
+    # same layout as the own kernels: `recv` still holds their verified result
+    api.lcb_check(lib.lcb_compare_bytes(tr.data_ptr(), recv.ptr, G * chunk, resb.ptr, native), "cmp")
+    stream.memcpy(got, resb, 16)
+    stream.run()
+    out["alltoall_nccl"]["verified"] = int(got[0]) == 0
     del ts, tr
     bsz = 4 * GiB
-    tb = torch.empty(bsz, dtype=torch.uint8, device="cuda")
+    tb = torch.zeros(bsz, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()  # torch's fill runs on torch's stream; the generator below on this library's
     if rank == 0:
-        tb.random_(0, 256)
+        api.lcb_check(lib.lcb_fill_splitmix64(tb.data_ptr(), bsz, 3, native), "fill")
+        stream.run()
     for _ in range(2):
         dist.broadcast(tb, 0)
     barrier()
+    nb = max(2, steps // 2)
     ev0.record()
-    for _ in range(max(2, steps // 2)):
+    for _ in range(nb):
         dist.broadcast(tb, 0)
     ev1.record()
     torch.cuda.synchronize()
-    ms = max_over_ranks(ev0.elapsed_time(ev1) / max(2, steps // 2))
+    ms = max_over_ranks(ev0.elapsed_time(ev1) / nb)
     report("broadcast_nccl_4GiB", bsz, ms)
+    expect = api.DeviceBuffer(bsz)
+    api.lcb_check(lib.lcb_fill_splitmix64(expect.ptr, bsz, 3, native), "fill")
+    api.lcb_check(lib.lcb_compare_bytes(tb.data_ptr(), expect.ptr, bsz, resb.ptr, native), "cmp")
+    stream.memcpy(got, resb, 16)
+    stream.run()
+    out["broadcast_nccl_4GiB"]["verified"] = int(got[0]) == 0
+    expect.free()
     del tb
     barrier()
     mr.close_peers(dist, peers)
@@ -490,6 +535,9 @@ def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_r
     barrier()
     for b in (send, recv, resb):
         b.free()
+    for name, entry in out.items():  # a check counts only if it held on every rank
+        if isinstance(entry, dict) and "verified" in entry:
+            entry["verified"] = max_over_ranks(0.0 if entry["verified"] else 1.0) == 0.0
     return out
 
 

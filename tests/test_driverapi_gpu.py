@@ -389,6 +389,7 @@ def test_config4_four_stream_ordering_1000_iterations(ctx, module):
     _four_stream_pipeline(ctx, n_elems=64 * 1024, iterations=1000, pinned=False)
 
 
-def test_config4_four_stream_ordering_full_buffers(ctx, module):
+def test_config4_four_stream_ordering_full_size(ctx, module):
+    # the full configuration: 64 MiB float32 per copy, 4 streams, 1000 iterations chained by cross-stream events
     _four_stream_pipeline.fn = module.function("axpb")
-    _four_stream_pipeline(ctx, n_elems=16 * MiB, iterations=40, pinned=True)   # 64 MiB per copy
+    _four_stream_pipeline(ctx, n_elems=16 * MiB, iterations=1000, pinned=True)
