@@ -172,6 +172,9 @@ struct Command {
 };
 
 constexpr int kSideLanes = 8;
+constexpr int kStageSlots = 4;                      // pinned bounce slots per stream for pageable host copies
+constexpr size_t kStageBytes = (size_t)8 << 20;    // bytes per slot
+constexpr size_t kStageMinBytes = (size_t)1 << 20; // smaller pageable copies go straight to the runtime
 
 }  // namespace lcu
 
@@ -184,6 +187,10 @@ struct LibreCUstream_ {
     cudaEvent_t fork = nullptr;
     int next_side = 0;
     std::vector<lcu::Command> pending;
+    void *stage[lcu::kStageSlots] = {};
+    cudaEvent_t stage_done[lcu::kStageSlots] = {};
+    bool stage_busy[lcu::kStageSlots] = {};
+    int stage_next = 0;
 };
 
 namespace lcu {
@@ -193,6 +200,10 @@ libreCudaStatus_t record(LibreCUstream stream, Command &&cmd);
 libreCudaStatus_t commence(LibreCUstream stream);
 libreCudaStatus_t host_wait_stream(LibreCUcontext ctx, cudaStream_t s);
 libreCudaStatus_t host_wait_event(LibreCUcontext ctx, cudaEvent_t e);
+bool is_pageable_host(const void *p);
+libreCudaStatus_t staged_h2d(LibreCUstream st, cudaStream_t lane, void *dst, const void *src, size_t bytes);
+libreCudaStatus_t staged_d2h(LibreCUstream st, cudaStream_t lane, void *dst, const void *src, size_t bytes);
+void free_ring(LibreCUstream st);
 }  // namespace lcu
 
 #define LCU_ENSURE_INIT() LIBRECUDA_VALIDATE(lcu::globals().initialized, LIBRECUDA_ERROR_NOT_INITIALIZED)

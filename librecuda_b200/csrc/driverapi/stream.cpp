@@ -92,7 +92,13 @@ static libreCudaStatus_t submit(LibreCUstream st, Command &c) {
             break;
         case Command::CopyEngine:
             LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
-            LCU_CUDA(cudaMemcpyAsync(c.dst, c.src, c.bytes, c.copy_kind, lane));
+            if (c.bytes >= kStageMinBytes && c.copy_kind == cudaMemcpyHostToDevice && is_pageable_host(c.src)) {
+                LIBRECUDA_ERR_PROPAGATE(staged_h2d(st, lane, c.dst, c.src, c.bytes));
+            } else if (c.bytes >= kStageMinBytes && c.copy_kind == cudaMemcpyDeviceToHost && is_pageable_host(c.dst)) {
+                LIBRECUDA_ERR_PROPAGATE(staged_d2h(st, lane, c.dst, c.src, c.bytes));
+            } else {
+                LCU_CUDA(cudaMemcpyAsync(c.dst, c.src, c.bytes, c.copy_kind, lane));
+            }
             break;
         case Command::Memset:
             LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
@@ -189,6 +195,7 @@ libreCudaStatus_t libreCuStreamDestroy(LibreCUstream stream) {
             }
         }
         (void)cudaStreamSynchronize(stream->main);
+        free_ring(stream);
         (void)cudaStreamDestroy(stream->main);
         (void)cudaEventDestroy(stream->fork);
     }

@@ -393,3 +393,26 @@ def test_config4_four_stream_ordering_full_size(ctx, module):
     # the full configuration: 64 MiB float32 per copy, 4 streams, 1000 iterations chained by cross-stream events
     _four_stream_pipeline.fn = module.function("axpb")
     _four_stream_pipeline(ctx, n_elems=16 * MiB, iterations=1000, pinned=True)
+
+
+@pytest.mark.parametrize("n", [MiB - 1, MiB, MiB + 1, 8 * MiB, 8 * MiB + 1, 32 * MiB + 5, 71 * MiB + 13])
+def test_pageable_host_copies_through_the_staging_ring(stream, n):
+    # ordinary (pageable) host memory on both sides, sizes around the slot (8 MiB) and ring (4 slots) boundaries
+    src = oracle.random_bytes(n + 3, seed=8)[3:]          # deliberately not page- or 16-byte aligned
+    back = np.zeros(n + 1, np.uint8)[1:]
+    d = api.DeviceBuffer(n + 64)
+    stream.memcpy(d.view(5), src, n)
+    stream.memcpy(back, d.view(5), n)
+    stream.run()
+    assert np.array_equal(back, src)
+    # interleaved directions and an async copy on a side lane share the same ring
+    back2 = np.zeros(n, np.uint8)
+    e = api.DeviceBuffer(n + 64)
+    stream.memcpy(e, src, n, async_=True)
+    stream.memcpy(back, d.view(5), n)
+    stream.memcpy(d, e, n)
+    stream.memcpy(back2, d, n)
+    stream.run()
+    assert np.array_equal(back, src) and np.array_equal(back2, src)
+    d.free()
+    e.free()
