@@ -26,7 +26,8 @@ enum lcbCopyPath {
     LCB_COPY_VEC = 1,   /* 16/32-byte vector loads+stores; src realigned by warp shuffle if needed */
     LCB_COPY_TMA = 2,   /* cp.async.bulk global->smem->global ring; needs (src-dst) % 16 == 0       */
     LCB_COPY_SMALL = 3, /* single small CTA wave, latency path                                     */
-    LCB_COPY_VEC32 = 4  /* 32-byte vector loads+stores; needs (src-dst) % 32 == 0                   */
+    LCB_COPY_VEC32 = 4, /* 32-byte vector loads+stores; needs (src-dst) % 32 == 0                   */
+    LCB_COPY_TMA2 = 5   /* bulk ring with separate load- and store-issuing threads; (src-dst) % 16 == 0 */
 };
 
 /* Device-to-device copy of `bytes` bytes, any alignment, any size (64-bit offsets).  Buffers must not

@@ -38,6 +38,8 @@ struct Tuning {
     int memset_smem_pad;     // same for the vector memset
     int fill_ctas_sm;        // CTAs per SM worth of grid for index fill / axpb
     int a2a_ctas_sm;         // CTAs per SM (all peers together) of the all-to-all push kernel
+    int tma2_depth;          // two-issuer ring: store groups that may still be reading shared memory
+    int copy_realign_retune; // 1: the realigning vector copy uses its own launch shape (256 x 8, 4 CTAs per SM)
 };
 Tuning &tuning();
 
@@ -128,6 +130,10 @@ __device__ __forceinline__ void mbar_init_fence() {
 
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
 }
 
 // Bounded wait for the phase with parity `parity`.  Returns false when it gives up.

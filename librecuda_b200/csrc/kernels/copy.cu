@@ -223,51 +223,137 @@ __global__ void __launch_bounds__(32) copy_tma_kernel(uint8_t *__restrict__ dst,
     }
     if (threadIdx.x != 0) return;
 
+    // Chunk c of the body belongs to CTA c % gridDim.x; this CTA's k-th chunk starts at (blockIdx.x + k * grid) * chunk.
+    // The issuing thread is the only one running, so everything in its loop is kept incremental: no division,
+    // no 64-bit multiply, stage and parity carried along.
     const size_t nchunks = (body + chunk - 1) / chunk;
     if ((size_t)blockIdx.x >= nchunks) return;
-    const size_t n_my = (nchunks - blockIdx.x + gridDim.x - 1) / gridDim.x;
-
+    const uint32_t n_my = (uint32_t)((nchunks - blockIdx.x + gridDim.x - 1) / gridDim.x);
+    const size_t stride = (size_t)gridDim.x * chunk;
     const uint32_t smem_base = smem_addr(smem);
     const uint32_t bar_base = smem_addr(bars);
 
     uint64_t pol = 0;
     if (HINT) pol = policy_evict_first();
 
-    auto chunk_off = [&](size_t k) { return ((size_t)blockIdx.x + k * gridDim.x) * (size_t)chunk; };
-    auto chunk_len = [&](size_t k) {
-        const size_t off = chunk_off(k);
-        const size_t rem = body - off;
-        return (uint32_t)(rem < chunk ? rem : chunk);
+    // load cursor
+    size_t ld_off = (size_t)blockIdx.x * chunk;
+    uint32_t ld_stage = 0, issued = 0;
+    auto issue_load = [&]() {
+        const size_t left = body - ld_off;
+        const uint32_t len = left < chunk ? (uint32_t)left : chunk;
+        const uint32_t bar = bar_base + 8 * ld_stage;
+        mbar_expect_tx(bar, len);
+        bulk_g2s<HINT>(smem_base + ld_stage * chunk, src + ld_off, len, bar, pol);
+        ld_off += stride;
+        ld_stage = (ld_stage + 1 == S) ? 0 : ld_stage + 1;
+        ++issued;
     };
-    auto issue_load = [&](size_t k) {
-        const int s = (int)(k % S);
-        const uint32_t len = chunk_len(k);
-        mbar_expect_tx(bar_base + 8 * s, len);
-        bulk_g2s<HINT>(smem_base + s * chunk, src + chunk_off(k), len, bar_base + 8 * s, pol);
-    };
+    while (issued < (uint32_t)L && issued < n_my) issue_load();
 
-    size_t issued = 0;
-    for (; issued < (size_t)L && issued < n_my; ++issued) issue_load(issued);
-
+    // store cursor
+    size_t st_off = (size_t)blockIdx.x * chunk;
+    uint32_t st_stage = 0, parity = 0, k = 0;
     bool ok = true;
-    size_t k = 0;
     for (; k < n_my; ++k) {
-        const int s = (int)(k % S);
-        const uint32_t parity = (uint32_t)((k / S) & 1);
-        if (!mbar_wait_bounded(bar_base + 8 * s, parity)) { ok = false; break; }
-        bulk_s2g<HINT>(dst + chunk_off(k), smem_base + s * chunk, chunk_len(k), pol);
+        if (!mbar_wait_bounded(bar_base + 8 * st_stage, parity)) { ok = false; break; }
+        const size_t left = body - st_off;
+        bulk_s2g<HINT>(dst + st_off, smem_base + st_stage * chunk, left < chunk ? (uint32_t)left : chunk, pol);
         bulk_commit();
+        st_off += stride;
+        if (++st_stage == S) {
+            st_stage = 0;
+            parity ^= 1;
+        }
         if (issued < n_my) {
-            if (issued >= (size_t)S) bulk_wait_read<S - L>();
-            issue_load(issued);
-            ++issued;
+            // the stage about to be reloaded was last read by the store S-L groups back
+            if (issued >= (uint32_t)S) bulk_wait_read<S - L>();
+            issue_load();
         }
     }
     if (!ok) {
         atomicOr(&g_error_word, kErrMbarrierTimeout);
         // loads already issued still target our shared memory: give each one more bounded wait
-        for (size_t j = k; j < issued; ++j) mbar_wait_bounded(bar_base + 8 * (int)(j % S), (uint32_t)((j / S) & 1));
+        for (uint32_t j = k; j < issued; ++j) mbar_wait_bounded(bar_base + 8 * (j % S), (j / S) & 1);
     }
+    bulk_wait_all();
+}
+
+
+// Two-issuer variant of the bulk ring: lane 0 of warp 0 only issues loads, lane 0 of warp 1 only issues
+// stores.  full[s] (complete_tx) tells the storer a stage is loaded; empty[s] (one arrival) tells the loader
+// that the store which last used the stage has finished reading it -- the storer learns that from
+// cp.async.bulk.wait_group.read D, D store groups behind its newest one.  Neither thread ever waits for the
+// other's kind of work, so twice as many bulk instructions can be in issue per SM.
+template <int S, int D, bool HINT>
+__global__ void __launch_bounds__(64) copy_tma2_kernel(uint8_t *__restrict__ dst, const uint8_t *__restrict__ src,
+                                                       size_t body, uint32_t chunk, Edges e) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    static_assert(D >= 1 && D < S, "the storer must release stages before the loader runs out of them");
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)S * chunk);
+    const uint32_t full_base = smem_addr(bars), empty_base = full_base + 8 * S;
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < 2 * S; ++s) mbar_init(full_base + 8 * s, 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    pdl_wait();
+    if (blockIdx.x == 0) {  // lanes 1..15 of warp 0 -> head bytes, lanes 1..15 of warp 1 -> tail bytes
+        const int t = threadIdx.x;
+        if (t >= 1 && t < 16 && t - 1 < e.head) e.dst[t - 1] = e.src[t - 1];
+        if (t >= 33 && t < 48 && t - 33 < e.tail) e.dst[e.tail_off + (t - 33)] = e.src[e.tail_off + (t - 33)];
+    }
+    if ((threadIdx.x & 31) != 0) return;
+
+    const size_t nchunks = (body + chunk - 1) / chunk;
+    if ((size_t)blockIdx.x >= nchunks) return;
+    const uint32_t n_my = (uint32_t)((nchunks - blockIdx.x + gridDim.x - 1) / gridDim.x);
+    const size_t stride = (size_t)gridDim.x * chunk;
+    const uint32_t smem_base = smem_addr(smem);
+    uint64_t pol = 0;
+    if (HINT) pol = policy_evict_first();
+    size_t off = (size_t)blockIdx.x * chunk;
+    uint32_t stage = 0, parity = 0;
+    bool ok = true;
+
+    if (threadIdx.x == 0) {  // ---- loader
+        for (uint32_t j = 0; j < n_my; ++j) {
+            // second and later trips round the ring wait for the stage to be released (phase j/S - 1)
+            if (j >= (uint32_t)S && !mbar_wait_bounded(empty_base + 8 * stage, parity ^ 1)) { ok = false; break; }
+            const size_t left = body - off;
+            const uint32_t len = left < chunk ? (uint32_t)left : chunk;
+            mbar_expect_tx(full_base + 8 * stage, len);
+            bulk_g2s<HINT>(smem_base + stage * chunk, src + off, len, full_base + 8 * stage, pol);
+            off += stride;
+            if (++stage == S) {
+                stage = 0;
+                parity ^= 1;
+            }
+        }
+        if (!ok) atomicOr(&g_error_word, kErrMbarrierTimeout);
+        return;
+    }
+    // ---- storer
+    uint32_t rel_stage = 0;  // stage of the chunk released next
+    for (uint32_t k = 0; k < n_my; ++k) {
+        if (!mbar_wait_bounded(full_base + 8 * stage, parity)) { ok = false; break; }
+        const size_t left = body - off;
+        bulk_s2g<HINT>(dst + off, smem_base + stage * chunk, left < chunk ? (uint32_t)left : chunk, pol);
+        bulk_commit();
+        off += stride;
+        if (++stage == S) {
+            stage = 0;
+            parity ^= 1;
+        }
+        if (k >= (uint32_t)D) {
+            bulk_wait_read<D>();  // store k-D no longer reads shared memory
+            mbar_arrive(empty_base + 8 * rel_stage);
+            rel_stage = (rel_stage + 1 == S) ? 0 : rel_stage + 1;
+        }
+    }
+    if (!ok) atomicOr(&g_error_word, kErrMbarrierTimeout);
     bulk_wait_all();
 }
 
@@ -374,8 +460,16 @@ int launch_vec_unroll(int unroll, int mode, int grid, int threads, cudaStream_t 
 
 int launch_vec(const Split &sp, int ctas, bool small, cudaStream_t st) {
     const Tuning &tu = tuning();
+    const bool realign = (reinterpret_cast<uintptr_t>(sp.src_body) & 15) != 0;
     int threads = small ? 128 : tu.copy_vec_threads;
     int unroll = small ? 1 : tu.copy_vec_unroll;
+    int ctas_sm = tu.copy_vec_ctas_sm;
+    if (realign && !small && tu.copy_realign_retune) {
+        // the shuffle path has more work per byte and measures best with more, smaller CTAs (6.47 vs 6.36 TB/s)
+        threads = 256;
+        unroll = 8;
+        ctas_sm = 4;
+    }
     if (!small) {
         // mid sizes: shrink the per-warp tile until every SM gets work
         const size_t want = (size_t)sm_count() * 2;
@@ -385,7 +479,7 @@ int launch_vec(const Split &sp, int ctas, bool small, cudaStream_t st) {
     const size_t per_cta = (size_t)unroll * threads;
     size_t need = (sp.nvec + per_cta - 1) / per_cta;
     if (need == 0) need = 1;
-    size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * tu.copy_vec_ctas_sm * (512 / threads);
+    size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * ctas_sm * (512 / threads);
     const int grid = (int)(need < cap ? need : cap);
 
     const uintptr_t sa = reinterpret_cast<uintptr_t>(sp.src_body);
@@ -465,6 +559,45 @@ int launch_tma(const Split &sp, int ctas, cudaStream_t st) {
     return 1;
 }
 
+
+template <int S, int D>
+int launch_tma2_cfg(bool hint, int grid, size_t smem, cudaStream_t st, uint8_t *d, const uint8_t *s, size_t body,
+                    uint32_t chunk, const Edges &e) {
+    if (hint) return launch_kernel(copy_tma2_kernel<S, D, true>, grid, 64, smem, st, d, s, body, chunk, e);
+    return launch_kernel(copy_tma2_kernel<S, D, false>, grid, 64, smem, st, d, s, body, chunk, e);
+}
+
+int launch_tma2(const Split &sp, int ctas, cudaStream_t st) {
+    const Tuning &tu = tuning();
+    const uint32_t chunk = (uint32_t)tu.tma_chunk;
+    if (chunk < 1024 || chunk > 65536 || (chunk & 127)) return 1;
+    const int S = tu.tma_stages, D = tu.tma2_depth;
+    const size_t smem = (size_t)S * chunk + 16 * S + (size_t)tu.tma_smem_pad;
+    if (smem > 227 * 1024) return 1;
+    const size_t body = sp.nvec * 16;
+    const size_t nchunks = (body + chunk - 1) / chunk;
+    const size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * tu.tma_ctas_sm;
+    const int grid = (int)(nchunks < cap ? (nchunks ? nchunks : 1) : cap);
+    uint8_t *d = reinterpret_cast<uint8_t *>(sp.dstv);
+    const bool hint = tu.tma_cache_hint != 0;
+#define LCB_TMA2_CFG(S_, D_) \
+    if (S == S_ && D == D_) return launch_tma2_cfg<S_, D_>(hint, grid, smem, st, d, sp.src_body, body, chunk, sp.e)
+    LCB_TMA2_CFG(4, 1);
+    LCB_TMA2_CFG(4, 2);
+    LCB_TMA2_CFG(8, 1);
+    LCB_TMA2_CFG(8, 2);
+    LCB_TMA2_CFG(8, 4);
+    LCB_TMA2_CFG(12, 2);
+    LCB_TMA2_CFG(12, 4);
+    LCB_TMA2_CFG(16, 2);
+    LCB_TMA2_CFG(16, 4);
+    LCB_TMA2_CFG(16, 8);
+    LCB_TMA2_CFG(24, 4);
+    LCB_TMA2_CFG(24, 8);
+#undef LCB_TMA2_CFG
+    return 1;
+}
+
 }  // namespace
 }  // namespace lcb
 
@@ -487,6 +620,9 @@ extern "C" int lcb_copy_d2d_ex(void *dst, const void *src, size_t bytes, int pat
         case LCB_COPY_TMA:
             if (!mutual) return 1;
             return launch_tma(sp, ctas, st);
+        case LCB_COPY_TMA2:
+            if (!mutual) return 1;
+            return launch_tma2(sp, ctas, st);
         case LCB_COPY_VEC32:
             if (((reinterpret_cast<uintptr_t>(dst) ^ reinterpret_cast<uintptr_t>(src)) & 31) != 0) return 1;
             return launch_vec32(dst, src, bytes, ctas, st);

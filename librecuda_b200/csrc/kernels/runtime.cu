@@ -32,6 +32,8 @@ static const Tuning kDefaults = {
         /*memset_smem_pad*/ 0,
         /*fill_ctas_sm*/ 64,
         /*a2a_ctas_sm*/ 1,
+        /*tma2_depth*/ 2,
+        /*copy_realign_retune*/ 1,
 };
 
 Tuning &tuning() {
@@ -91,6 +93,8 @@ extern "C" int lcb_tune(const char *name, int value) {
     LCB_KNOB(memset_smem_pad)
     LCB_KNOB(fill_ctas_sm)
     LCB_KNOB(a2a_ctas_sm)
+    LCB_KNOB(tma2_depth)
+    LCB_KNOB(copy_realign_retune)
 #undef LCB_KNOB
     return 1;
 }

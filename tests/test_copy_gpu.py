@@ -14,7 +14,7 @@ from gpu_util import GUARD, GUARD_BYTE, device_checksum, device_compare, to_devi
 
 pytestmark = pytest.mark.gpu
 MiB = 1 << 20
-AUTO, VEC, TMA, SMALL, VEC32 = 0, 1, 2, 3, 4
+AUTO, VEC, TMA, SMALL, VEC32, TMA2 = 0, 1, 2, 3, 4, 5
 GOLDEN = json.loads((Path(__file__).parent / "golden" / "ref_d2d_golden.json").read_text())
 
 
@@ -70,18 +70,30 @@ def test_all_sixteen_by_sixteen_phase_pairs(stream):
     _run_cases(stream, [(70000 + so, so, do) for so in range(16) for do in range(16)], AUTO)
 
 
-@pytest.mark.parametrize("path", [AUTO, VEC, TMA])
+@pytest.mark.parametrize("path", [AUTO, VEC, TMA, TMA2])
 def test_mid_and_large_sizes(stream, path):
     sizes = [MiB - 1, MiB, MiB + 131, 2 * MiB + 5, 3 * MiB + 4099, 16 * MiB + 4100, 64 * MiB + 17]
-    offs = [(0, 0), (64, 64), (16, 48)] if path == TMA else [(0, 0), (1, 0), (0, 3), (7, 7), (64, 1), (3, 64), (5, 9)]
+    offs = [(0, 0), (64, 64), (16, 48)] if path in (TMA, TMA2) else [(0, 0), (1, 0), (0, 3), (7, 7), (64, 1), (3, 64), (5, 9)]
     _run_cases(stream, [(n, so, do) for n in sizes for so, do in offs], path)
 
 
-def test_bulk_path_edges_and_small_bodies(stream):
+@pytest.mark.parametrize("path", [TMA, TMA2])
+def test_bulk_path_edges_and_small_bodies(stream, path):
     # congruent but not 16-byte aligned pointers: head and tail bytes ride along with the bulk ring
     cases = [(n, o, o + 16 * k) for n in (0, 1, 15, 16, 17, 31, 33, 1000, 16384, 16385, 3 * 16384 + 7, 200001)
              for o in (0, 1, 5, 15) for k in (0, 2)]
-    _run_cases(stream, cases, TMA)
+    _run_cases(stream, cases, path)
+
+
+@pytest.mark.parametrize("knobs", [dict(tma_stages=4, tma2_depth=1, tma_chunk=4096), dict(tma_stages=8, tma2_depth=4, tma_chunk=16384),
+                                   dict(tma_stages=16, tma2_depth=8, tma_chunk=8192, tma_cache_hint=1),
+                                   dict(tma_stages=24, tma2_depth=4, tma_chunk=8192)])
+def test_two_issuer_ring_configurations(stream, knobs):
+    try:
+        api.tune(**knobs)
+        _run_cases(stream, [(n, o, o) for n in (5 * MiB + 48, 333333, 65536 * 7, 40 * MiB + 16) for o in (0, 16)], TMA2)
+    finally:
+        api.tune_reset()
 
 
 def test_bulk_path_rejects_mutually_misaligned(stream):
@@ -101,7 +113,8 @@ def test_32_byte_vector_path(stream):
                                    dict(tma_stages=8, tma_lookahead=6, tma_chunk=16384, tma_cache_hint=1),
                                    dict(tma_stages=16, tma_lookahead=12, tma_chunk=8192, tma_ctas_sm=1),
                                    dict(tma_stages=3, tma_lookahead=2, tma_chunk=65536),
-                                   dict(tma_stages=6, tma_lookahead=3, tma_chunk=32768, tma_ctas_sm=1)])
+                                   dict(tma_stages=6, tma_lookahead=3, tma_chunk=32768, tma_ctas_sm=1),
+                                   dict(tma_stages=12, tma_lookahead=8, tma_chunk=4096)])
 def test_bulk_ring_configurations(stream, knobs):
     try:
         api.tune(**knobs)
@@ -127,7 +140,7 @@ def test_tiny_grids_cover_everything(stream):
     src_h = oracle.random_bytes(n, seed=7)
     s, d = api.DeviceBuffer(n + 64), api.DeviceBuffer(n + 64)
     to_device(stream, s, src_h)
-    for path, ctas, so, do in [(VEC, 1, 0, 0), (VEC, 3, 1, 0), (TMA, 1, 16, 32), (TMA, 5, 0, 0)]:
+    for path, ctas, so, do in [(VEC, 1, 0, 0), (VEC, 3, 1, 0), (TMA, 1, 16, 32), (TMA, 5, 0, 0), (TMA2, 1, 0, 16), (TMA2, 7, 0, 0)]:
         to_device(stream, d, np.zeros(n + 64, np.uint8))
         _copy(stream, d.ptr + do, s.ptr + so, n - 64, path, ctas)
         got = to_host(stream, d, n + 64)
