@@ -110,6 +110,11 @@ size_t lcb_checksum64_noalloc_max_bytes(void);
  * up: 0 = no error.  Synchronises the device. */
 int lcb_device_error_word(unsigned int *out);
 
+/* Loads the default copy / memset / fill kernels onto the current device now instead of at their first
+ * launch.  ref: loadMemcpyKernelsIfNeeded, driverapi/src/memcopy.cpp:23-75, called from context creation
+ * (driverapi/src/librecuda.cpp:622). */
+int lcb_preload(void);
+
 /* Library / build identification: "lcb200 <version> sm_100a". */
 const char *lcb_version(void);
 

@@ -222,6 +222,7 @@ libreCudaStatus_t libreCuCtxCreate_v2(LibreCUcontext *pCtx, int flags, LibreCUde
     LCU_CUDA(cudaFree(nullptr));  // forces creation of the primary context
     LCU_CUDA(cudaEventCreate(&ctx->epoch));
     LCU_CUDA(cudaEventRecord(ctx->epoch, nullptr));
+    LCU_LCB(lcb_preload());  // the reference loads its copy kernels here as well (librecuda.cpp:622)
     globals().current = ctx.get();  // reference: librecuda.cpp:619
     *pCtx = ctx.release();
     LIBRECUDA_SUCCEED();

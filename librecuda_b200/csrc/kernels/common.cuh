@@ -43,6 +43,8 @@ struct Tuning {
 };
 Tuning &tuning();
 
+int preload_copy_kernels();  // force-load the default copy / fill kernels on the current device
+int preload_fill_kernels();
 int sm_count();            // SMs of the current device (cached per device)
 int check_launch();        // cudaGetLastError() as int
 

@@ -601,6 +601,23 @@ int launch_tma2(const Split &sp, int ctas, cudaStream_t st) {
 }  // namespace
 }  // namespace lcb
 
+namespace lcb {
+// With lazy module loading a kernel is loaded at its first launch; touching the default instantiations here
+// moves that cost out of the first copy (the reference loads its copy kernels when a context is created,
+// driverapi/src/librecuda.cpp:622).
+int preload_copy_kernels() {
+    cudaFuncAttributes a;
+    cudaError_t e = cudaFuncGetAttributes(&a, copy_vec_kernel<-1, 4, 2>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<-1, 1, 2>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<0, 8, 2>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<1, 8, 2>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<2, 8, 2>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<3, 8, 2>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_tma_kernel<8, 6, false>);
+    return (int)e;
+}
+}  // namespace lcb
+
 extern "C" int lcb_copy_d2d_ex(void *dst, const void *src, size_t bytes, int path, int ctas, lcbStream stream) {
     using namespace lcb;
     if (bytes == 0) return 0;

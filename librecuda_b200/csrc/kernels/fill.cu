@@ -231,6 +231,16 @@ int memset_any(void *dst, uint32_t pattern, int elem, size_t count, int path, in
 }  // namespace
 }  // namespace lcb
 
+namespace lcb {
+int preload_fill_kernels() {
+    cudaFuncAttributes a;
+    cudaError_t e = cudaFuncGetAttributes(&a, memset_vec_kernel<8>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, memset_vec_kernel<1>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, index_fill_kernel);
+    return (int)e;
+}
+}  // namespace lcb
+
 extern "C" int lcb_memset_ex(void *dst, unsigned int value, int elem_bytes, size_t count, int path, int ctas,
                              lcbStream stream) {
     uint32_t pattern;

@@ -99,6 +99,12 @@ extern "C" int lcb_tune(const char *name, int value) {
     return 1;
 }
 
+extern "C" int lcb_preload(void) {
+    int rc = lcb::preload_copy_kernels();
+    if (rc == 0) rc = lcb::preload_fill_kernels();
+    return rc;
+}
+
 extern "C" const char *lcb_version(void) { return "lcb200 0.1 sm_100a"; }
 
 // ---- event timers on a raw stream ---------------------------------------------------------------

@@ -3,6 +3,7 @@
     python -m librecuda_b200.profile_case copy   [--bytes N] [--reps R] [--path auto|vec|tma|vec32] [--src-off A] [--dst-off B]
     python -m librecuda_b200.profile_case memset [--bytes N] [--reps R] [--path auto|vec|bulk]
     python -m librecuda_b200.profile_case index_fill | axpb | checksum | alltoall_self
+    python -m librecuda_b200.profile_case sweep  [--max-log2 33]     (timing table, not for a profiler)
 
 The default 256 MiB per buffer is larger than the 126 MB L2 (DRAM counters stay meaningful) and small
 enough for a multi-pass capture to finish in about a minute.  Prints the CUDA-event time per launch.
@@ -18,15 +19,64 @@ PATHS = {"auto": 0, "vec": 1, "tma": 2, "small": 3, "vec32": 4}
 MEMSET_PATHS = {"auto": 0, "vec": 1, "bulk": 2}
 
 
+def sweep(max_log2: int):
+    """DtoD copy and memset GB/s for sizes 4 KiB .. 2^max_log2 and a few src/dst byte offsets, timed with CUDA
+    events over back-to-back launches (best of 3 batches).  Copies count read + write bytes."""
+    lib = api.lib
+    api.Context(0)
+    st = api.Stream()
+    nat = st.native
+    top = 1 << max_log2
+    a, b = api.DeviceBuffer(top + 256), api.DeviceBuffer(top + 256)
+    api.lcb_check(lib.lcb_fill_splitmix64(a.ptr, top, 1, nat), "fill")
+    st.memset_d8(b, 0, top)
+    st.run()
+    t = api.Timer()
+
+    def timed(fn, reps):
+        for _ in range(3):
+            api.lcb_check(fn(), "launch")
+        best = 1e30
+        for _ in range(3):
+            t.start(nat)
+            for _ in range(reps):
+                api.lcb_check(fn(), "launch")
+            t.stop(nat)
+            best = min(best, t.elapsed_ms() / reps)
+        return best
+
+    offsets = [(0, 0), (1, 0), (0, 3), (7, 7), (64, 1)]
+    print("| bytes | " + " | ".join(f"copy src+{so} dst+{do}" for so, do in offsets) + " | memset D8 | us per aligned copy |")
+    print("|---|" + "---|" * (len(offsets) + 2))
+    for k in range(12, max_log2 + 1):
+        n = 1 << k
+        reps = 200 if n <= (16 << 20) else (20 if n <= (1 << 30) else 5)
+        cells = []
+        us = 0.0
+        for so, do in offsets:
+            ms = timed(lambda: lib.lcb_copy_d2d(b.ptr + do, a.ptr + so, n, nat), reps)
+            if (so, do) == (0, 0):
+                us = ms * 1e3
+            cells.append(f"{2 * n / (ms * 1e-3) / 1e9:.1f}")
+        ms = timed(lambda: lib.lcb_memset_d8(b.ptr, 0x5A, n, nat), reps)
+        cells.append(f"{n / (ms * 1e-3) / 1e9:.1f}")
+        print(f"| {n} | " + " | ".join(cells) + f" | {us:.1f} |", flush=True)
+    assert api.device_error_word() == 0
+    t.destroy()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["copy", "memset", "index_fill", "axpb", "checksum", "alltoall_self"])
+    ap.add_argument("kernel", choices=["copy", "memset", "index_fill", "axpb", "checksum", "alltoall_self", "sweep"])
+    ap.add_argument("--max-log2", type=int, default=33)
     ap.add_argument("--bytes", type=int, default=256 << 20)
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--path", default="auto")
     ap.add_argument("--src-off", type=int, default=0)
     ap.add_argument("--dst-off", type=int, default=0)
     args = ap.parse_args()
+    if args.kernel == "sweep":
+        return sweep(args.max_log2)
     lib = api.lib
     api.Context(0)
     st = api.Stream()
