@@ -1,9 +1,13 @@
 // Process-wide state of the kernel layer: tunables, cached device properties, the sticky device error
 // word, and the small timing helpers the benchmark uses on raw CUDA streams.
+#include <cstdlib>
 #include <cstring>
+#include <string>
 
 #include "common.cuh"
 #include "lcb200_kernels.h"
+
+extern "C" int lcb_tune(const char *name, int value);
 
 namespace lcb {
 
@@ -38,6 +42,22 @@ static const Tuning kDefaults = {
 
 Tuning &tuning() {
     static Tuning t = kDefaults;
+    static bool env_read = false;
+    if (!env_read) {  // LCB_TUNE="knob=value,knob=value": overrides for experiments, applied once
+        env_read = true;
+        if (const char *e = std::getenv("LCB_TUNE")) {
+            std::string all(e);
+            size_t pos = 0;
+            while (pos < all.size()) {
+                size_t end = all.find(',', pos);
+                if (end == std::string::npos) end = all.size();
+                const std::string item = all.substr(pos, end - pos);
+                const size_t eq = item.find('=');
+                if (eq != std::string::npos) lcb_tune(item.substr(0, eq).c_str(), std::atoi(item.c_str() + eq + 1));
+                pos = end + 1;
+            }
+        }
+    }
     return t;
 }
 

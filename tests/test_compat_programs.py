@@ -37,3 +37,11 @@ def test_reference_program(name):
         assert bad not in text, text[-2000:]
     for want in EXPECT[name]:
         assert want in text, text[-2000:]
+    if name == "async_kernels":
+        # five async launches of the ~100 ms kernel must overlap; five ordered ones must not
+        import re
+
+        took = {k: int(v) for k, v in re.findall(r"(Single|5xAsync|5xSync) kernel took: (\d+)ms", text)}
+        assert set(took) == {"Single", "5xAsync", "5xSync"}, text[-2000:]
+        assert took["5xAsync"] < 0.6 * took["5xSync"], took
+        assert took["5xSync"] > 3 * took["Single"] * 0.8, took

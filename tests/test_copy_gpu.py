@@ -64,6 +64,16 @@ def test_small_sizes_all_alignment_classes(stream, path):
     _run_cases(stream, cases, path)
 
 
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_random_sizes_and_offsets(stream, seed):
+    rng = np.random.default_rng(seed)
+    cases = []
+    for _ in range(400):
+        n = int(2 ** rng.uniform(0, 23))           # 1 byte .. 8 MiB, log-uniform
+        cases.append((n + int(rng.integers(0, 17)), int(rng.integers(0, 64)), int(rng.integers(0, 64))))
+    _run_cases(stream, cases, AUTO)
+
+
 def test_all_sixteen_by_sixteen_phase_pairs(stream):
     cases = [(1000 + 3 * so + do, so, do) for so in range(16) for do in range(16)]
     _run_cases(stream, cases, VEC)
