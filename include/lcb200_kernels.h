@@ -110,6 +110,11 @@ size_t lcb_checksum64_noalloc_max_bytes(void);
  * up: 0 = no error.  Synchronises the device. */
 int lcb_device_error_word(unsigned int *out);
 
+/* Exercises the give-up path of the kernels' bounded waits without any fault: one thread waits, at most
+ * max_tries (1..100000) tries, on a barrier nothing completes, then sets bit 0 of the sticky error word and
+ * returns.  Afterwards lcb_device_error_word reports 1 and the device is fully usable. */
+int lcb_selftest_wait_timeout(unsigned int max_tries, lcbStream stream);
+
 /* Loads the default copy / memset / fill kernels onto the current device now instead of at their first
  * launch.  ref: loadMemcpyKernelsIfNeeded, driverapi/src/memcopy.cpp:23-75, called from context creation
  * (driverapi/src/librecuda.cpp:622). */

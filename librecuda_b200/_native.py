@@ -42,6 +42,7 @@ LCB_FUNCTIONS = {
     "lcb_checksum64_noalloc_max_bytes": (sz, []),
     "lcb_device_error_word": (i32, [C.POINTER(C.c_uint)]),
     "lcb_preload": (i32, []),
+    "lcb_selftest_wait_timeout": (i32, [C.c_uint, vp]),
     "lcb_version": (C.c_char_p, []),
     "lcb_tune": (i32, [C.c_char_p, i32]),
     "lcb_timer_create": (i32, [vpp]),

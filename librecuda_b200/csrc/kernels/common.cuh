@@ -139,9 +139,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 
 // Bounded wait for the phase with parity `parity`.  Returns false when it gives up.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    constexpr uint32_t kMaxTries = 1u << 22;  // each try may itself suspend for a hardware-chosen time
-    for (uint32_t i = 0; i < kMaxTries; ++i) {
+constexpr uint32_t kMbarMaxTries = 1u << 22;  // each try may itself suspend for a hardware-chosen time
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t max_tries = kMbarMaxTries) {
+    for (uint32_t i = 0; i < max_tries; ++i) {
         uint32_t ok;
         asm volatile(
             "{\n"

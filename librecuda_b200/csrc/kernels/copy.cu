@@ -602,6 +602,25 @@ int launch_tma2(const Split &sp, int ctas, cudaStream_t st) {
 }  // namespace lcb
 
 namespace lcb {
+// Self-test of the give-up path of the bounded wait: waits on a barrier that nothing ever completes, with a
+// small try limit, then does exactly what the bulk ring does when a wait runs out (sticky error bit, return).
+// Nothing faults and nothing hangs; the context stays usable.
+__global__ void wait_timeout_selftest_kernel(uint32_t max_tries) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x != 0) return;
+    mbar_init(smem_addr(&bar), 1);
+    mbar_init_fence();
+    if (!mbar_wait_bounded(smem_addr(&bar), 0, max_tries)) atomicOr(&g_error_word, kErrMbarrierTimeout);
+}
+}  // namespace lcb
+
+extern "C" int lcb_selftest_wait_timeout(unsigned int max_tries, lcbStream stream) {
+    if (max_tries == 0 || max_tries > 100000u) return 1;  // keeps the self-test in the millisecond range
+    lcb::wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(max_tries);
+    return lcb::check_launch();
+}
+
+namespace lcb {
 // With lazy module loading a kernel is loaded at its first launch; touching the default instantiations here
 // moves that cost out of the first copy (the reference loads its copy kernels when a context is created,
 // driverapi/src/librecuda.cpp:622).

@@ -176,6 +176,19 @@ def test_reference_golden_vectors(stream, case):
     d.free()
 
 
+def test_bounded_wait_gives_up_with_an_error_status_and_the_device_stays_usable(stream):
+    # failure detection without a fault: a wait that can never be satisfied runs out of tries, the kernel
+    # reports it through the sticky error word and returns
+    assert api.device_error_word() == 0
+    assert api.lib.lcb_selftest_wait_timeout(0, stream.native) == 1          # limits are enforced on the host
+    assert api.lib.lcb_selftest_wait_timeout(10**7, stream.native) == 1
+    api.lcb_check(api.lib.lcb_selftest_wait_timeout(2000, stream.native), "selftest")
+    assert api.device_error_word() == 1      # reported ...
+    assert api.device_error_word() == 0      # ... and cleared by the read
+    _run_cases(stream, [(3 * MiB + 5, 0, 0), (MiB, 1, 2)], AUTO)   # copies still work afterwards
+    _run_cases(stream, [(5 * MiB + 48, 16, 16)], TMA)
+
+
 def test_device_helpers_agree_with_oracle(stream):
     n = 3 * MiB + 5
     buf, res = api.DeviceBuffer(n + 8), api.DeviceBuffer(16)
