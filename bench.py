@@ -275,6 +275,10 @@ def run_ours(args):
         t_ms = timed_loop(api, stream, fn, steps)
         also[name] = {"GBps": round(nbytes / (t_ms * 1e-3) / 1e9, 1), "ms": round(t_ms, 4), "note": "CUDA runtime's own path, for comparison"}
 
+    ref_gpu = reference_kernel_on_gpu(api, stream, src, dst, steps)
+    if ref_gpu is not None:
+        also["reference_HighBW_kernel_sm100a_128MiB"] = ref_gpu
+
     # end to end through the public API with HOST buffers: HtoD -> DtoD -> DtoH inside the timed region
     e2e = run_e2e(api, ctx, n, max(2, min(steps, 10)), max_over_ranks, barrier, world)
 
@@ -309,6 +313,40 @@ def run_ours(args):
         dist.barrier()
         dist.destroy_process_group()
     return 0 if verified else 1
+
+
+def reference_kernel_on_gpu(api, stream, src, dst, steps):
+    """The reference's own HighBW copy kernel (driverapi/kernels/memcpy/memcpy.cu, compiled for sm_100a from the
+    reference checkout into oracle/_ref/ at build time) at the largest size its dispatcher launches correctly,
+    128 MiB with grid (size/4096, 1) x 256 threads (driverapi/src/memcopy.cpp:93-107), beside this library's
+    copy of the same 128 MiB.  Returns None when the image is not there."""
+    cubin = ROOT / "oracle" / "_ref" / "ref_memcpy_sm100a.cubin"
+    if not cubin.exists():
+        return None
+    n = 128 * MiB
+    mod = api.Module(cubin.read_bytes())
+    fn = mod.function("memcpyKernelHighBW")
+    start, end = api.Event(), api.Event()
+
+    def timed(record_one):
+        for _ in range(3):
+            record_one()
+        stream.run()
+        start.record(stream)
+        for _ in range(steps):
+            record_one()
+        end.record(stream)
+        stream.run()
+        return api.elapsed_ms(start, end) / steps
+
+    ms_ref = timed(lambda: stream.launch(fn, (n // 4096, 1, 1), (256, 1, 1), 0, [C.c_void_p(dst.ptr), C.c_void_p(src.ptr)]))
+    ms_own = timed(lambda: stream.memcpy(dst, src, n))
+    for e in (start, end):
+        e.destroy()
+    mod.unload()
+    gb = lambda ms: round(2.0 * n / (ms * 1e-3) / 1e9, 1)
+    return {"reference_kernel_GBps": gb(ms_ref), "this_library_GBps": gb(ms_own), "bytes": n,
+            "note": "both through libreCuLaunchKernel / libreCuMemCpy on one stream, timed with libreCuEvent*"}
 
 
 def run_e2e(api, ctx, n, steps, max_over_ranks, barrier, world):

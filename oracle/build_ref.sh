@@ -19,6 +19,13 @@ if [ -d "$ref/driverapi/src" ]; then
       -x none "$here/ref_shim.cpp" \
       -o "$here/_ref/libref_memcopy.so"
   echo "built $here/_ref/libref_memcopy.so"
+  # the same kernel source as a real sm_100a image, so the reference's kernels can run on the B200 beside
+  # this library's (launched with the reference's grid shapes by tests and, for timing, by bench.py)
+  nvcc="${CUDA_HOME:-/usr/local/cuda}/bin/nvcc"
+  if [ -x "$nvcc" ]; then
+    "$nvcc" -cubin -gencode arch=compute_100a,code=sm_100a -O3 -o "$here/_ref/ref_memcpy_sm100a.cubin" "$d/kernels/memcpy/memcpy.cu"
+    echo "built $here/_ref/ref_memcpy_sm100a.cubin"
+  fi
 else
   echo "no reference checkout at $ref: skipping oracle/_ref"
 fi
