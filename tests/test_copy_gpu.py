@@ -251,4 +251,4 @@ def test_dtod_sweep_powers_of_two_all_offset_pairs(stream):
 
 def test_dtod_sweep_largest_sizes(stream):
     # 2, 4 and 8 GiB: 64-bit offsets everywhere (the reference over-launches from 256 MiB on)
-    _sweep(stream, [1 << 31, 1 << 32, 1 << 33], [(0, 0), (1, 0), (0, 3), (7, 64), (64, 64)])
+    _sweep(stream, [1 << 31, 1 << 32, 1 << 33], [(a, b) for a in SWEEP_OFFSETS for b in SWEEP_OFFSETS])
