@@ -13,14 +13,14 @@ constexpr unsigned int kErrMbarrierTimeout = 1u;
 
 // Tunables reachable through lcb_tune() (for sweeps; the defaults are the shipped configuration).
 struct Tuning {
-    int copy_vec_threads;   // threads per CTA of the vector copy kernel
+    int copy_vec_threads;   // threads per CTA of the vector copy kernel (0 with unroll 0: chosen by size)
     int copy_vec_unroll;    // 16-byte vectors in flight per thread
-    int copy_vec_ctas_sm;   // resident CTAs per SM assumed when sizing the persistent grid
+    int copy_vec_ctas_sm;   // 0: one short CTA per tile; > 0: persistent grid of this many CTAs per SM
     int copy_cache_mode;    // 0: ld.cs/st.cs   1: default caching   2: L1::no_allocate
     int tma_chunk;          // bytes per bulk copy
     int tma_stages;         // ring depth
     int tma_lookahead;      // loads in flight ahead of the store
-    int tma_ctas_sm;        // CTAs per SM of the bulk ring kernels
+    int tma_ctas_sm;        // 0: one chunk per CTA; > 0: persistent ring, this many CTAs per SM
     int tma_cache_hint;     // 0: none  1: evict_first policy on loads and stores
     int auto_tma_min_mib;   // LCB_COPY_AUTO uses the bulk ring from this many MiB on (congruent pointers only; -1 never)
     int memset_path;        // 0 auto, 1 vector, 2 bulk
@@ -36,10 +36,12 @@ struct Tuning {
     int copy_vec_smem_pad;   // extra dynamic shared memory per CTA of the vector copy (caps CTAs per SM)
     int tma_smem_pad;        // same for the bulk ring
     int memset_smem_pad;     // same for the vector memset
-    int fill_ctas_sm;        // CTAs per SM worth of grid for index fill / axpb
+    int fill_ctas_sm;        // CTAs per SM worth of grid for the index fill (write-only: one short CTA per tile is best)
+    int axpb_ctas_sm;        // same for y = a*x + b (read + write: fewer, longer CTAs are best)
     int a2a_ctas_sm;         // CTAs per SM (all peers together) of the all-to-all push kernel
     int tma2_depth;          // two-issuer ring: store groups that may still be reading shared memory
-    int copy_realign_retune; // 1: the realigning vector copy uses its own launch shape (256 x 8, 4 CTAs per SM)
+    int tma2_stages;         // two-issuer ring: stages
+    int tma2_chunk;          // two-issuer ring: bytes per bulk copy
 };
 Tuning &tuning();
 

@@ -461,17 +461,27 @@ int launch_vec_unroll(int unroll, int mode, int grid, int threads, cudaStream_t 
 int launch_vec(const Split &sp, int ctas, bool small, cudaStream_t st) {
     const Tuning &tu = tuning();
     const bool realign = (reinterpret_cast<uintptr_t>(sp.src_body) & 15) != 0;
-    int threads = small ? 128 : tu.copy_vec_threads;
-    int unroll = small ? 1 : tu.copy_vec_unroll;
-    int ctas_sm = tu.copy_vec_ctas_sm;
-    if (realign && !small && tu.copy_realign_retune) {
-        // the shuffle path has more work per byte and measures best with more, smaller CTAs (6.47 vs 6.36 TB/s)
-        threads = 256;
-        unroll = 8;
-        ctas_sm = 4;
+    // Launch shape.  Measured on B200: one SHORT CTA per tile -- a grid as large as the tile count, scheduled by
+    // the hardware as SMs free up -- beats a persistent grid at every size above L2 (7.0 vs 6.65 TB/s at
+    // 1 GiB).  Best tile: 128 threads x 2 vectors (4 KiB) from ~100 MiB to a few GiB, 512 x 4 (32 KiB)
+    // below that, for the realigning path and for the very largest copies.
+    const size_t bytes = sp.nvec * 16;
+    int threads, unroll;
+    if (small) {
+        threads = 128;
+        unroll = 1;
+    } else if (tu.copy_vec_threads > 0 && tu.copy_vec_unroll > 0) {
+        threads = tu.copy_vec_threads;
+        unroll = tu.copy_vec_unroll;
+    } else if (!realign && bytes >= ((size_t)96 << 20) && bytes <= ((size_t)4 << 30)) {
+        threads = 128;
+        unroll = 2;
+    } else {
+        threads = 512;
+        unroll = 4;
     }
     if (!small) {
-        // mid sizes: shrink the per-warp tile until every SM gets work
+        // mid sizes: shrink the tile until every SM gets work
         const size_t want = (size_t)sm_count() * 2;
         while (unroll > 1 && (sp.nvec / ((size_t)unroll * threads)) < want) unroll >>= 1;
         while (threads > 128 && (sp.nvec / ((size_t)unroll * threads)) < want) threads >>= 1;
@@ -479,7 +489,10 @@ int launch_vec(const Split &sp, int ctas, bool small, cudaStream_t st) {
     const size_t per_cta = (size_t)unroll * threads;
     size_t need = (sp.nvec + per_cta - 1) / per_cta;
     if (need == 0) need = 1;
-    size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * ctas_sm * (512 / threads);
+    // copy_vec_ctas_sm > 0 (or an explicit `ctas`) caps the grid and makes the CTAs loop (persistent form)
+    size_t cap = ctas > 0 ? (size_t)ctas
+                 : tu.copy_vec_ctas_sm > 0 ? (size_t)sm_count() * tu.copy_vec_ctas_sm * (512 / threads)
+                                           : ((size_t)1 << 30);
     const int grid = (int)(need < cap ? need : cap);
 
     const uintptr_t sa = reinterpret_cast<uintptr_t>(sp.src_body);
@@ -510,12 +523,12 @@ int launch_vec32(void *dst, const void *src, size_t bytes, int ctas, cudaStream_
     e.head = (int)head;
     e.tail = (int)(bytes - head - n32 * 32);
     e.tail_off = head + n32 * 32;
-    const int threads = tu.copy_vec_threads;
-    const int unroll = tu.copy_vec_unroll >= 4 ? 4 : 2;
+    const int threads = tu.copy_vec_threads > 0 ? tu.copy_vec_threads : 512;
+    const int unroll = tu.copy_vec_unroll == 2 ? 2 : 4;
     const size_t per_cta = (size_t)unroll * threads;
     size_t need = (n32 + per_cta - 1) / per_cta;
     if (need == 0) need = 1;
-    size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * tu.copy_vec_ctas_sm * (512 / threads);
+    size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * (tu.copy_vec_ctas_sm > 0 ? tu.copy_vec_ctas_sm : 1) * (512 / threads);
     const int grid = (int)(need < cap ? need : cap);
     if (unroll == 4) return launch_kernel(copy_vec32_kernel<4>, grid, threads, 0, st, d + head, s + head, n32, e);
     return launch_kernel(copy_vec32_kernel<2>, grid, threads, 0, st, d + head, s + head, n32, e);
@@ -538,7 +551,8 @@ int launch_tma(const Split &sp, int ctas, cudaStream_t st) {
     if (smem > 227 * 1024) return 1;
     const size_t body = sp.nvec * 16;
     const size_t nchunks = (body + chunk - 1) / chunk;
-    size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * tu.tma_ctas_sm;
+    // tma_ctas_sm == 0: one chunk per CTA (short CTAs, 7.0 TB/s); > 0: persistent ring of that many CTAs per SM
+    size_t cap = ctas > 0 ? (size_t)ctas : tu.tma_ctas_sm > 0 ? (size_t)sm_count() * tu.tma_ctas_sm : ((size_t)1 << 30);
     int grid = (int)(nchunks < cap ? (nchunks ? nchunks : 1) : cap);
     uint8_t *d = reinterpret_cast<uint8_t *>(sp.dstv);
     const bool hint = tu.tma_cache_hint != 0;
@@ -569,14 +583,14 @@ int launch_tma2_cfg(bool hint, int grid, size_t smem, cudaStream_t st, uint8_t *
 
 int launch_tma2(const Split &sp, int ctas, cudaStream_t st) {
     const Tuning &tu = tuning();
-    const uint32_t chunk = (uint32_t)tu.tma_chunk;
+    const uint32_t chunk = (uint32_t)tu.tma2_chunk;
     if (chunk < 1024 || chunk > 65536 || (chunk & 127)) return 1;
-    const int S = tu.tma_stages, D = tu.tma2_depth;
+    const int S = tu.tma2_stages, D = tu.tma2_depth;
     const size_t smem = (size_t)S * chunk + 16 * S + (size_t)tu.tma_smem_pad;
     if (smem > 227 * 1024) return 1;
     const size_t body = sp.nvec * 16;
     const size_t nchunks = (body + chunk - 1) / chunk;
-    const size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * tu.tma_ctas_sm;
+    const size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * (tu.tma_ctas_sm > 0 ? tu.tma_ctas_sm : 1);
     const int grid = (int)(nchunks < cap ? (nchunks ? nchunks : 1) : cap);
     uint8_t *d = reinterpret_cast<uint8_t *>(sp.dstv);
     const bool hint = tu.tma_cache_hint != 0;
@@ -627,12 +641,13 @@ namespace lcb {
 int preload_copy_kernels() {
     cudaFuncAttributes a;
     cudaError_t e = cudaFuncGetAttributes(&a, copy_vec_kernel<-1, 4, 2>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<-1, 2, 2>);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<-1, 1, 2>);
-    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<0, 8, 2>);
-    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<1, 8, 2>);
-    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<2, 8, 2>);
-    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<3, 8, 2>);
-    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_tma_kernel<8, 6, false>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<0, 4, 2>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<1, 4, 2>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<2, 4, 2>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<3, 4, 2>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_tma_kernel<2, 1, false>);
     return (int)e;
 }
 }  // namespace lcb

@@ -284,8 +284,8 @@ extern "C" int lcb_axpb_f32(float *y, const float *x, float a, float b, size_t c
     const bool vec = ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(x)) & 15) == 0;
     const int threads = 512;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (vec) return launch_kernel(axpb_kernel<true>, grid_for(count / 4 + 1, threads, tuning().fill_ctas_sm), threads, 0, st, y, x, a, b, count);
-    return launch_kernel(axpb_kernel<false>, grid_for(count, threads, 4), threads, 0, st, y, x, a, b, count);
+    if (vec) return launch_kernel(axpb_kernel<true>, grid_for(count / 4 + 1, threads, tuning().axpb_ctas_sm), threads, 0, st, y, x, a, b, count);
+    return launch_kernel(axpb_kernel<false>, grid_for(count, threads, tuning().axpb_ctas_sm), threads, 0, st, y, x, a, b, count);
 }
 
 extern "C" int lcb_fill_splitmix64(void *dst, size_t bytes, uint64_t seed, lcbStream stream) {

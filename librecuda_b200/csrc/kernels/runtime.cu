@@ -12,20 +12,20 @@ extern "C" int lcb_tune(const char *name, int value);
 namespace lcb {
 
 static const Tuning kDefaults = {
-        /*copy_vec_threads*/ 512,
-        /*copy_vec_unroll*/ 4,
-        /*copy_vec_ctas_sm*/ 1,
+        /*copy_vec_threads*/ 0,
+        /*copy_vec_unroll*/ 0,
+        /*copy_vec_ctas_sm*/ 0,
         /*copy_cache_mode*/ 2,
-        /*tma_chunk*/ 8192,
-        /*tma_stages*/ 8,
-        /*tma_lookahead*/ 6,
-        /*tma_ctas_sm*/ 1,
+        /*tma_chunk*/ 32768,
+        /*tma_stages*/ 2,
+        /*tma_lookahead*/ 1,
+        /*tma_ctas_sm*/ 0,
         /*tma_cache_hint*/ 0,
-        /*auto_tma_min_mib*/ 512,
+        /*auto_tma_min_mib*/ 4097,
         /*memset_path*/ 0,
         /*memset_unroll*/ 8,
         /*memset_threads*/ 256,
-        /*memset_ctas_sm*/ 64,
+        /*memset_ctas_sm*/ 4096,
         /*memset_chunk*/ 32768,
         /*memset_issuers*/ 4,
         /*memset_bulk_ctas_sm*/ 2,
@@ -34,10 +34,12 @@ static const Tuning kDefaults = {
         /*copy_vec_smem_pad*/ 0,
         /*tma_smem_pad*/ 0,
         /*memset_smem_pad*/ 0,
-        /*fill_ctas_sm*/ 64,
+        /*fill_ctas_sm*/ 4096,
+        /*axpb_ctas_sm*/ 64,
         /*a2a_ctas_sm*/ 1,
         /*tma2_depth*/ 2,
-        /*copy_realign_retune*/ 1,
+        /*tma2_stages*/ 8,
+        /*tma2_chunk*/ 8192,
 };
 
 Tuning &tuning() {
@@ -112,9 +114,11 @@ extern "C" int lcb_tune(const char *name, int value) {
     LCB_KNOB(tma_smem_pad)
     LCB_KNOB(memset_smem_pad)
     LCB_KNOB(fill_ctas_sm)
+    LCB_KNOB(axpb_ctas_sm)
     LCB_KNOB(a2a_ctas_sm)
     LCB_KNOB(tma2_depth)
-    LCB_KNOB(copy_realign_retune)
+    LCB_KNOB(tma2_stages)
+    LCB_KNOB(tma2_chunk)
 #undef LCB_KNOB
     return 1;
 }

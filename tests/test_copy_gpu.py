@@ -95,9 +95,9 @@ def test_bulk_path_edges_and_small_bodies(stream, path):
     _run_cases(stream, cases, path)
 
 
-@pytest.mark.parametrize("knobs", [dict(tma_stages=4, tma2_depth=1, tma_chunk=4096), dict(tma_stages=8, tma2_depth=4, tma_chunk=16384),
-                                   dict(tma_stages=16, tma2_depth=8, tma_chunk=8192, tma_cache_hint=1),
-                                   dict(tma_stages=24, tma2_depth=4, tma_chunk=8192)])
+@pytest.mark.parametrize("knobs", [dict(tma2_stages=4, tma2_depth=1, tma2_chunk=4096), dict(tma2_stages=8, tma2_depth=4, tma2_chunk=16384),
+                                   dict(tma2_stages=16, tma2_depth=8, tma2_chunk=8192, tma_cache_hint=1),
+                                   dict(tma2_stages=24, tma2_depth=4, tma2_chunk=8192)])
 def test_two_issuer_ring_configurations(stream, knobs):
     try:
         api.tune(**knobs)
@@ -119,7 +119,7 @@ def test_32_byte_vector_path(stream):
     _run_cases(stream, cases, VEC32)
 
 
-@pytest.mark.parametrize("knobs", [dict(tma_stages=4, tma_lookahead=2, tma_chunk=8192),
+@pytest.mark.parametrize("knobs", [dict(tma_stages=8, tma_lookahead=6, tma_chunk=8192, tma_ctas_sm=1), dict(tma_stages=4, tma_lookahead=2, tma_chunk=8192),
                                    dict(tma_stages=8, tma_lookahead=6, tma_chunk=16384, tma_cache_hint=1),
                                    dict(tma_stages=16, tma_lookahead=12, tma_chunk=8192, tma_ctas_sm=1),
                                    dict(tma_stages=3, tma_lookahead=2, tma_chunk=65536),
@@ -133,8 +133,9 @@ def test_bulk_ring_configurations(stream, knobs):
         api.tune_reset()
 
 
-@pytest.mark.parametrize("knobs", [dict(copy_vec_unroll=1), dict(copy_vec_unroll=2), dict(copy_vec_unroll=8),
-                                   dict(copy_vec_threads=256, copy_cache_mode=1), dict(copy_cache_mode=2),
+@pytest.mark.parametrize("knobs", [dict(copy_vec_threads=512, copy_vec_unroll=1), dict(copy_vec_threads=256, copy_vec_unroll=2),
+                                   dict(copy_vec_threads=512, copy_vec_unroll=8), dict(copy_vec_threads=256, copy_vec_unroll=4, copy_cache_mode=1),
+                                   dict(copy_cache_mode=0), dict(copy_vec_threads=512, copy_vec_unroll=4, copy_vec_ctas_sm=1),
                                    dict(copy_vec_threads=128, copy_vec_unroll=8, copy_vec_ctas_sm=2)])
 def test_vector_kernel_configurations(stream, knobs):
     try:
