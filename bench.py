@@ -38,9 +38,9 @@ UNIT = "GB/s"
 NVLINK_NOMINAL = 900.0   # GB/s per direction per GPU
 NVLINK_MEASURED = 770.0  # GB/s, peer copy measured on this pool
 # dram__bytes_read.sum + dram__bytes_write.sum of one copy launch, from the 256 MiB ncu capture summarised in
-# profiles/copy_kernels_256MiB_ncu.md: reads equal the source, writes equal the destination less ~47 MB that
+# profiles/copy_kernels_256MiB_ncu.md: reads equal the source, writes equal the destination less ~50 MB that
 # is still dirty in L2 at kernel exit (a constant, not a fraction)
-NCU_TRAFFIC_1GIB = 2 * GiB - 47_000_000
+NCU_TRAFFIC_1GIB = 2 * GiB - 50_000_000
 
 
 def measured_hbm_peak():
@@ -247,11 +247,11 @@ def run_ours(args):
 
     peak, peak_kind = measured_hbm_peak()
     achieved = 2.0 * n / (ms_local * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "lcb_copy_d2d (1 GiB, 16-byte aligned)", "achieved": round(achieved, 1),
+    roofline = {"bound": "hbm", "kernel": "lcb_copy_d2d -> copy_vec_kernel<-1,2,2>, 262144 CTAs x 128 threads (1 GiB, 16-byte aligned)", "achieved": round(achieved, 1),
                 "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
                 "frac_of_nominal_8000": round(achieved / 8000.0, 4), "traffic": NCU_TRAFFIC_1GIB,
                 "traffic_note": "dram read+write bytes per 1 GiB launch: ncu capture at 256 MiB (reads = source size, "
-                                "writes = destination size minus ~47 MB left dirty in L2), constant term kept"}
+                                "writes = destination size minus ~50 MB left dirty in L2), constant term kept"}
 
     # other single-GPU paths of the metric: memset D32 and index fill over 1 GiB (bytes written counted once)
     also = {}
