@@ -36,7 +36,7 @@ static const Tuning kDefaults = {
         /*memset_smem_pad*/ 0,
         /*fill_ctas_sm*/ 4096,
         /*axpb_ctas_sm*/ 64,
-        /*a2a_ctas_sm*/ 1,
+        /*a2a_ctas_sm*/ 4096,
         /*tma2_depth*/ 2,
         /*tma2_stages*/ 8,
         /*tma2_chunk*/ 8192,
