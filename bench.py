@@ -37,9 +37,9 @@ METRIC = "dtod_copy_GBps"
 UNIT = "GB/s"
 NVLINK_NOMINAL = 900.0   # GB/s per direction per GPU
 NVLINK_MEASURED = 770.0  # GB/s, peer copy measured on this pool
-# dram__bytes_read.sum + dram__bytes_write.sum of one copy launch, from the 256 MiB ncu capture summarised in
-# profiles/copy_kernels_256MiB_ncu.md: reads equal the source, writes equal the destination less ~50 MB that
-# is still dirty in L2 at kernel exit (a constant, not a fraction)
+# dram__bytes_read.sum + dram__bytes_write.sum of one copy launch, from an ncu capture of the same kernel at
+# 256 MiB: reads equal the source, writes equal the destination less ~50 MB that is still dirty in L2 at kernel
+# exit (a constant, not a fraction)
 NCU_TRAFFIC_1GIB = 2 * GiB - 50_000_000
 
 

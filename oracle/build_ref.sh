@@ -2,7 +2,7 @@
 # Builds the oracle's C restatement and, when a reference checkout is available, the reference's own DtoD
 # dispatcher + kernels compiled for the host (oracle/_ref/libref_memcopy.so).  Reference sources are
 # compiled where they lie; nothing is copied.  TEST INFRASTRUCTURE ONLY.
-#   usage: oracle/build_ref.sh [reference-checkout]      (default: $LIBRECUDA_REFERENCE or /root/reference)
+#   usage: oracle/build_ref.sh [reference-checkout]      (default: $LIBRECUDA_REFERENCE, else the build machine's reference mount)
 set -euo pipefail
 here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 ref="${1:-${LIBRECUDA_REFERENCE:-/root/reference}}"
