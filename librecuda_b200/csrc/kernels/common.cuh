@@ -37,7 +37,7 @@ struct Tuning {
     int tma_smem_pad;        // same for the bulk ring
     int memset_smem_pad;     // same for the vector memset
     int fill_ctas_sm;        // CTAs per SM worth of grid for the index fill (write-only: one short CTA per tile is best)
-    int axpb_ctas_sm;        // same for y = a*x + b (read + write: fewer, longer CTAs are best)
+    int axpb_ctas_sm;        // same for the vector form of y = a*x + b
     int a2a_ctas_sm;         // grid cap of the all-to-all kernel in CTAs per SM, all peers together (large: one short CTA per tile, 709 vs 692 GB/s)
     int tma2_depth;          // two-issuer ring: store groups that may still be reading shared memory
     int tma2_stages;         // two-issuer ring: stages

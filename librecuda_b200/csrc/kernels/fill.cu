@@ -115,28 +115,46 @@ __global__ void __launch_bounds__(512) index_fill_kernel(float *__restrict__ dst
     }
 }
 
-template <bool VEC>
+// VEC: both pointers 16-byte aligned.  Tile = U vectors per thread; all loads of a tile are issued before its
+// stores, and the launcher sizes the grid to one short CTA per tile (see the copy kernels).
+template <bool VEC, int U>
 __global__ void __launch_bounds__(512) axpb_kernel(float *__restrict__ y, const float *__restrict__ x, float a, float b,
                                                    size_t count) {
     pdl_launch_dependents();
     pdl_wait();
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (VEC) {
         const size_t nvec = count / 4;
         const uint4 *x4 = reinterpret_cast<const uint4 *>(x);
         uint4 *y4 = reinterpret_cast<uint4 *>(y);
-        for (size_t j = tid; j < nvec; j += stride) {
-            uint4 v = ld_stream<0>(x4 + j);
-            v.x = __float_as_uint(__fadd_rn(__fmul_rn(a, __uint_as_float(v.x)), b));
-            v.y = __float_as_uint(__fadd_rn(__fmul_rn(a, __uint_as_float(v.y)), b));
-            v.z = __float_as_uint(__fadd_rn(__fmul_rn(a, __uint_as_float(v.z)), b));
-            v.w = __float_as_uint(__fadd_rn(__fmul_rn(a, __uint_as_float(v.w)), b));
-            st_stream<0>(y4 + j, v);
+        const size_t tile = (size_t)U * blockDim.x;
+        const size_t ntiles = (nvec + tile - 1) / tile;
+        for (size_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+            const size_t base = t * tile + threadIdx.x;
+            uint4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const size_t j = base + (size_t)u * blockDim.x;
+                v[u] = (j < nvec) ? ld_stream<2>(x4 + j) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const size_t j = base + (size_t)u * blockDim.x;
+                uint4 w = v[u];
+                w.x = __float_as_uint(__fadd_rn(__fmul_rn(a, __uint_as_float(w.x)), b));
+                w.y = __float_as_uint(__fadd_rn(__fmul_rn(a, __uint_as_float(w.y)), b));
+                w.z = __float_as_uint(__fadd_rn(__fmul_rn(a, __uint_as_float(w.z)), b));
+                w.w = __float_as_uint(__fadd_rn(__fmul_rn(a, __uint_as_float(w.w)), b));
+                if (j < nvec) st_stream<2>(y4 + j, w);
+            }
         }
-        for (size_t i = nvec * 4 + tid; i < count; i += stride) y[i] = __fadd_rn(__fmul_rn(a, x[i]), b);
+        if (blockIdx.x == 0) {  // up to three trailing elements
+            const size_t i = nvec * 4 + threadIdx.x;
+            if (i < count) y[i] = __fadd_rn(__fmul_rn(a, x[i]), b);
+        }
     } else {
-        for (size_t i = tid; i < count; i += stride) y[i] = __fadd_rn(__fmul_rn(a, x[i]), b);
+        const size_t stride = (size_t)gridDim.x * blockDim.x;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride)
+            y[i] = __fadd_rn(__fmul_rn(a, x[i]), b);
     }
 }
 
@@ -282,10 +300,16 @@ extern "C" int lcb_axpb_f32(float *y, const float *x, float a, float b, size_t c
     if (y == nullptr || x == nullptr) return 1;
     if ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(x)) & 3) return 1;
     const bool vec = ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(x)) & 15) == 0;
-    const int threads = 512;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (vec) return launch_kernel(axpb_kernel<true>, grid_for(count / 4 + 1, threads, tuning().axpb_ctas_sm), threads, 0, st, y, x, a, b, count);
-    return launch_kernel(axpb_kernel<false>, grid_for(count, threads, tuning().axpb_ctas_sm), threads, 0, st, y, x, a, b, count);
+    if (vec) {
+        // one short CTA per tile of 128 threads x 2 vectors (4 KiB), like the copy kernel it resembles
+        const int threads = 128;
+        const size_t tiles = (count / 4 + 2 * threads - 1) / (2 * threads);
+        const size_t cap = (size_t)sm_count() * tuning().axpb_ctas_sm;
+        const int grid = (int)(tiles == 0 ? 1 : (tiles < cap ? tiles : cap));
+        return launch_kernel(axpb_kernel<true, 2>, grid, threads, 0, st, y, x, a, b, count);
+    }
+    return launch_kernel(axpb_kernel<false, 1>, grid_for(count, 512, 64), 512, 0, st, y, x, a, b, count);
 }
 
 extern "C" int lcb_fill_splitmix64(void *dst, size_t bytes, uint64_t seed, lcbStream stream) {

@@ -35,7 +35,7 @@ static const Tuning kDefaults = {
         /*tma_smem_pad*/ 0,
         /*memset_smem_pad*/ 0,
         /*fill_ctas_sm*/ 4096,
-        /*axpb_ctas_sm*/ 64,
+        /*axpb_ctas_sm*/ 16384,
         /*a2a_ctas_sm*/ 4096,
         /*tma2_depth*/ 2,
         /*tma2_stages*/ 8,
