@@ -26,6 +26,11 @@ static libreCudaStatus_t describe(LibreCUFunction f) {
         f->param_size.push_back(size);
         if (off + size > f->param_bytes) f->param_bytes = off + size;
     }
+    // With lazy module loading the code of a function is brought onto the device at its first launch (about
+    // 10 us); asking for an attribute loads it now, so that the cost is paid in libreCuModuleLoadData -- where
+    // the reference uploads its image too (librecuda.cpp:1376) -- and not inside the first Commence.
+    int regs = 0;
+    LCU_CU(drv->FuncGetAttribute(&regs, /*CU_FUNC_ATTRIBUTE_NUM_REGS*/ 4, f->fn));
     LIBRECUDA_SUCCEED();
 }
 
