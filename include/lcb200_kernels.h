@@ -23,8 +23,8 @@ typedef void *lcbStream; /* cudaStream_t / CUstream */
 /* Copy-path selector for lcb_copy_d2d_ex (lcb_copy_d2d always uses LCB_COPY_AUTO). */
 enum lcbCopyPath {
     LCB_COPY_AUTO = 0,  /* pick by size and alignment                                             */
-    LCB_COPY_VEC = 1,   /* 16/32-byte vector loads+stores; src realigned by warp shuffle if needed */
-    LCB_COPY_TMA = 2,   /* cp.async.bulk global->smem->global ring; needs (src-dst) % 16 == 0       */
+    LCB_COPY_VEC = 1,   /* 16-byte vector loads+stores; src realigned by warp shuffle if needed   */
+    LCB_COPY_TMA = 2,   /* cp.async.bulk global->smem->global; needs (src-dst) % 16 == 0            */
     LCB_COPY_SMALL = 3, /* single small CTA wave, latency path                                     */
     LCB_COPY_VEC32 = 4, /* 32-byte vector loads+stores; needs (src-dst) % 32 == 0                   */
     LCB_COPY_TMA2 = 5   /* bulk ring with separate load- and store-issuing threads; (src-dst) % 16 == 0 */
@@ -36,7 +36,8 @@ enum lcbCopyPath {
  * memcpyKernelLowLatency / memcpyKernelTrailing, driverapi/kernels/memcpy/memcpy.cu:5-27. */
 int lcb_copy_d2d(void *dst, const void *src, size_t bytes, lcbStream stream);
 
-/* Same copy with an explicit path and grid (ctas = 0 selects the default persistent grid).  An
+/* Same copy with an explicit path and grid (ctas = 0: the default grid, one short CTA per tile; ctas > 0:
+ * exactly that many CTAs, looping over the tiles).  An
  * infeasible request (LCB_COPY_TMA with mutually misaligned pointers) returns 1. */
 int lcb_copy_d2d_ex(void *dst, const void *src, size_t bytes, int path, int ctas, lcbStream stream);
 

@@ -6,16 +6,18 @@
 //
 //   dst:  [ head < 16 B ][ body: nvec 16-byte vectors, dst 16-byte aligned ][ tail < 16 B ]
 //
-//  * copy_vec_kernel    persistent grid, each lane keeps U 16-byte loads in flight before storing.
+//  * copy_vec_kernel    each lane keeps U 16-byte loads in flight before storing; launched as one short CTA
+//                       per tile (the hardware deals tiles to SMs in address order as they free up).
 //                       If src is not congruent to dst mod 16 the lanes load ALIGNED source vectors and
 //                       rebuild each output vector from their own vector and their right neighbour's,
 //                       fetched with one warp shuffle per word (lane 0 supplies the first vector of the
 //                       next row), then a funnel shift for the sub-word part.  No misaligned access is
 //                       ever issued; DRAM traffic stays at the algorithmic 2 bytes per byte copied.
-//  * copy_tma_kernel    for mutually aligned spans: one thread per CTA drives a ring of bulk copies
-//                       (cp.async.bulk global->shared with mbarrier complete_tx, then shared->global in
-//                       bulk groups).  Non-multicast forms only, so the same kernel is usable with a peer
-//                       GPU's memory on either side.
+//  * copy_tma_kernel    for mutually aligned spans: one thread per CTA moves its chunks through shared
+//                       memory with bulk copies (cp.async.bulk global->shared with mbarrier complete_tx,
+//                       then shared->global in bulk groups); by default one 32 KiB chunk per CTA, or a
+//                       persistent multi-stage ring.  Non-multicast forms only, so the same kernel is
+//                       usable with a peer GPU's memory on either side.
 //  * alltoall_kernel     one launch that moves every chunk of an all-to-all between this GPU and all its
 //                       peers (the copy fused with the exchange), by remote loads (pull) or stores (push).
 #include "common.cuh"

@@ -3,7 +3,7 @@
 // The reference has no memset (driverapi/include/librecuda.h:37-114); its fill kernels are the test
 // fixtures tests/indexing/write_float.cu:1-4 (one scalar store per thread over a 1-D grid) and
 // tests/write_float/write_float.cu:1-7.  Here:
-//  * memset_vec_kernel   persistent grid of 16-byte streaming stores, U stores per lane per iteration.
+//  * memset_vec_kernel   16-byte streaming stores, U per lane per tile; one short CTA per tile by default.
 //  * memset_bulk_kernel  fills ONE shared-memory tile with the pattern, then one thread per warp replays it
 //                        with bulk stores (cp.async.bulk shared->global); the SM issues one instruction
 //                        per `chunk` bytes written.
