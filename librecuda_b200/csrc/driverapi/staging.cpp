@@ -31,6 +31,15 @@ CopyPool &pool() {
 
 }  // namespace
 
+// bit 0: non-temporal stores when draining a slot into the user's buffer (DtoH); bit 1: when filling a slot (HtoD)
+static int nt_mode() {
+    static int mode = [] {
+        const char *e = std::getenv("LIBRECUDA_STAGING_NT");
+        return e ? std::atoi(e) : 1;
+    }();
+    return mode;
+}
+
 bool is_pageable_host(const void *p) {
     cudaPointerAttributes attr{};
     if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
@@ -60,7 +69,7 @@ libreCudaStatus_t staged_h2d(LibreCUstream st, cudaStream_t lane, void *dst, con
         const int slot = st->stage_next;
         st->stage_next = (slot + 1) % kStageSlots;
         if (st->stage_busy[slot]) LCU_CUDA(cudaEventSynchronize(st->stage_done[slot]));
-        pool().copy(st->stage[slot], s + off, n);
+        pool().copy(st->stage[slot], s + off, n, /*streaming=*/(nt_mode() & 2) != 0);
         LCU_CUDA(cudaMemcpyAsync(d + off, st->stage[slot], n, cudaMemcpyHostToDevice, lane));
         LCU_CUDA(cudaEventRecord(st->stage_done[slot], lane));
         st->stage_busy[slot] = true;
@@ -85,7 +94,7 @@ libreCudaStatus_t staged_d2h(LibreCUstream st, cudaStream_t lane, void *dst, con
         head = (head + 1) % kStageSlots;
         --count;
         LCU_CUDA(cudaEventSynchronize(st->stage_done[p.slot]));
-        pool().copy(d + p.off, st->stage[p.slot], p.n);
+        pool().copy(d + p.off, st->stage[p.slot], p.n, /*streaming=*/(nt_mode() & 1) != 0);
         st->stage_busy[p.slot] = false;
         LIBRECUDA_SUCCEED();
     };

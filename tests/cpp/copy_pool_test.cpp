@@ -18,7 +18,7 @@ int main() {
                 for (size_t off : {(size_t)0, (size_t)63}) {
                     std::fill(dst.begin(), dst.end(), 0xAA);
                     std::fill(want.begin(), want.end(), 0xAA);
-                    pool.copy(dst.data() + off, src.data() + 7, n);
+                    pool.copy(dst.data() + off, src.data() + 7, n, /*streaming=*/(round & 1) != 0);
                     std::memcpy(want.data() + off, src.data() + 7, n);
                     if (dst != want) {
                         std::printf("mismatch: workers %d size %zu off %zu\n", workers, n, off);
