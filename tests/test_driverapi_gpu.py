@@ -416,3 +416,25 @@ def test_pageable_host_copies_through_the_staging_ring(stream, n):
     assert np.array_equal(back, src) and np.array_equal(back2, src)
     d.free()
     e.free()
+
+
+def test_host_copies_beyond_4_gib(stream):
+    # the reference rejects HtoD/DtoH transfers of UINT32_MAX bytes or more (driverapi/src/cmdqueue.cpp:735)
+    from gpu_util import device_checksum
+
+    n = (1 << 32) + 4096 + 3
+    words = (n + 7) // 8
+    host = np.arange(words, dtype=np.uint64).view(np.uint8)[:n]       # cheap to make, position-dependent
+    dev = api.DeviceBuffer(n + 8)
+    scratch, out = api.DeviceBuffer(api.lib.lcb_checksum_scratch_bytes()), api.DeviceBuffer(8)
+    stream.memcpy(dev, host, n)
+    stream.run()
+    assert device_checksum(stream, dev.ptr, n, scratch, out) == oracle.checksum64(host)
+    back = np.zeros(n, np.uint8)
+    stream.memcpy(back, dev, n)
+    stream.run()
+    assert np.array_equal(back[:4096], host[:4096]) and np.array_equal(back[-8192:], host[-8192:])
+    assert np.array_equal(back[(1 << 32) - 64:(1 << 32) + 64], host[(1 << 32) - 64:(1 << 32) + 64])
+    assert oracle.checksum64(back) == oracle.checksum64(host)
+    for b in (dev, scratch, out):
+        b.free()
