@@ -466,7 +466,8 @@ int launch_vec(const Split &sp, int ctas, bool small, cudaStream_t st) {
     // Launch shape.  Measured on B200: one SHORT CTA per tile -- a grid as large as the tile count, scheduled by
     // the hardware as SMs free up -- beats a persistent grid at every size above L2 (7.0 vs 6.65 TB/s at
     // 1 GiB).  Best tile: 128 threads x 2 vectors (4 KiB) from ~100 MiB to a few GiB, 512 x 4 (32 KiB)
-    // below that, for the realigning path and for the very largest copies.
+    // below that, for the realigning path and for the very largest copies (congruent pointers go to the
+    // bulk-copy kernel from 2 GiB on, see lcb_copy_d2d_ex).
     const size_t bytes = sp.nvec * 16;
     int threads, unroll;
     if (small) {

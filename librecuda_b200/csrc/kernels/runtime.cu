@@ -21,7 +21,7 @@ static const Tuning kDefaults = {
         /*tma_lookahead*/ 1,
         /*tma_ctas_sm*/ 0,
         /*tma_cache_hint*/ 0,
-        /*auto_tma_min_mib*/ 4097,
+        /*auto_tma_min_mib*/ 2048,
         /*memset_path*/ 0,
         /*memset_unroll*/ 8,
         /*memset_threads*/ 256,
