@@ -14,6 +14,7 @@
 #include <chrono>
 #include <cstdlib>
 #include <cstring>
+#include <iterator>
 #include <thread>
 
 #include "internal.h"
@@ -160,10 +161,19 @@ libreCudaStatus_t commence(LibreCUstream st) {
     }
     std::vector<Command> batch;
     batch.swap(st->pending);
-    for (Command &c : batch) LIBRECUDA_ERR_PROPAGATE(submit(st, c));
+    libreCudaStatus_t status = LIBRECUDA_SUCCESS;
+    for (size_t i = 0; i < batch.size(); ++i) {
+        status = submit(st, batch[i]);
+        if (status != LIBRECUDA_SUCCESS) {
+            // the failed operation is dropped; what was recorded after it stays recorded for a later Commence
+            st->pending.insert(st->pending.begin(), std::make_move_iterator(batch.begin() + (long)i + 1),
+                               std::make_move_iterator(batch.end()));
+            break;
+        }
+    }
     LibreCUcontext cur = globals().current;
     if (cur != nullptr && cur != st->ctx) LIBRECUDA_ERR_PROPAGATE(bind(cur));
-    LIBRECUDA_SUCCEED();
+    return status;
 }
 
 }  // namespace lcu

@@ -438,3 +438,20 @@ def test_host_copies_beyond_4_gib(stream):
     assert oracle.checksum64(back) == oracle.checksum64(host)
     for b in (dev, scratch, out):
         b.free()
+
+
+def test_failed_submission_drops_only_the_failed_operation(stream, module):
+    # a launch the driver rejects on the host (dynamic shared memory above 48 KiB without the opt-in attribute):
+    # Commence reports the error, the operations recorded after it are kept for the next Commence
+    a_h, b_h = np.full(4096, 7, np.uint8), np.full(4096, 9, np.uint8)
+    a, b = api.DeviceBuffer(4096), api.DeviceBuffer(4096)
+    out = api.DeviceBuffer(4)
+    stream.memcpy(a, a_h, 4096)
+    stream.launch(module.function("store_value"), (1, 1, 1), (1, 1, 1), 100 * 1024, [C.c_void_p(out.ptr), C.c_float(1.0)])
+    stream.memcpy(b, b_h, 4096)
+    st = lib.libreCuStreamCommence(stream.handle)
+    assert st != api.SUCCESS
+    stream.run()          # submits what was left
+    assert (to_host(stream, a, 4096) == 7).all() and (to_host(stream, b, 4096) == 9).all()
+    for x in (a, b, out):
+        x.free()
