@@ -128,6 +128,8 @@ const char *lcb_version(void);
  * fields of the Tuning record in the kernel sources; "reset" restores the shipped configuration).
  * For sweeps; returns 1 for an unknown name. */
 int lcb_tune(const char *name, int value);
+/* Current value of a tunable (-1 for an unknown name). */
+int lcb_tune_get(const char *name);
 
 /* CUDA-event stopwatch on a raw stream: start/stop record events on `stream`, elapsed waits for the
  * stop event and returns milliseconds. */

@@ -45,6 +45,7 @@ LCB_FUNCTIONS = {
     "lcb_selftest_wait_timeout": (i32, [C.c_uint, vp]),
     "lcb_version": (C.c_char_p, []),
     "lcb_tune": (i32, [C.c_char_p, i32]),
+    "lcb_tune_get": (i32, [C.c_char_p]),
     "lcb_timer_create": (i32, [vpp]),
     "lcb_timer_start": (i32, [vp, vp]),
     "lcb_timer_stop": (i32, [vp, vp]),

@@ -273,10 +273,13 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
         LCU_NCCL(n, n->GroupEnd());
         return rebind_current();
     }
-    // Own path, two phases of remote loads (the faster direction while the root only sends).  The buffer is cut into one shard
-    // per non-root device.  Phase 1: device g pulls shard g from the root (every byte leaves the root once).
-    // Phase 2: every non-root device pulls the other shards from the devices that own them, so that traffic
-    // is spread over all NVLink ports instead of the root's alone.
+    // Own path.  The buffer is cut into one shard per non-root device, each shard into pieces.
+    //   pull lane of device g : loads piece after piece of shard g from the root (every byte leaves the root
+    //                           exactly once; remote loads are the faster direction while the root only sends);
+    //   push lane of device g : as soon as a piece has landed, stores it to every other non-root device (with
+    //                           all those links busy in both directions, stores are the faster form).
+    // The two lanes are separate CUDA streams tied by one event per piece, so forwarding piece p overlaps the
+    // arrival of piece p+1 and the whole broadcast takes about one buffer's worth of link time.
     std::vector<int> owners;
     for (int g = 0; g < nDev; ++g)
         if (g != root) owners.push_back(g);
@@ -285,29 +288,75 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
     LIBRECUDA_ERR_PROPAGATE(libreCuPartitionPlan(byteCount, parts, 0, off));
     LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
     const uint8_t *src = static_cast<const uint8_t *>(bufs[root]);
-    std::vector<cudaEvent_t> landed(parts, nullptr);
-    for (int k = 0; k < parts; ++k) {
-        const int g = owners[k];
-        if (off[k + 1] == off[k]) continue;
-        LIBRECUDA_ERR_PROPAGATE(bind(streams[g]->ctx));
-        LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[g]) + off[k], src + off[k], off[k + 1] - off[k], streams[g]->main));
-        LCU_CUDA(cudaEventCreateWithFlags(&landed[k], cudaEventDisableTiming));
-        LCU_CUDA(cudaEventRecord(landed[k], streams[g]->main));
-    }
-    for (int kq = 0; kq < parts; ++kq) {
-        const int q = owners[kq];
-        LIBRECUDA_ERR_PROPAGATE(bind(streams[q]->ctx));
-        for (int step = 1; step < parts; ++step) {  // rotate the order so the pulls spread over the owners
-            const int k = (kq + step) % parts;
-            if (landed[k] == nullptr) continue;
-            const int g = owners[k];
-            LCU_CUDA(cudaStreamWaitEvent(streams[q]->main, landed[k], 0));
-            LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[q]) + off[k], static_cast<const uint8_t *>(bufs[g]) + off[k],
-                                 off[k + 1] - off[k], streams[q]->main));
+    // one piece when there is nobody to forward to; otherwise pipelined pieces (64 MiB by default)
+    const int piece_mib = lcb_tune_get("bcast_piece_mib") > 0 ? lcb_tune_get("bcast_piece_mib") : 64;
+    const int pull_ctas = lcb_tune_get("bcast_pull_ctas") > 0 ? lcb_tune_get("bcast_pull_ctas") : 74;
+    // Programmatic dependent launch parks the next kernel's CTAs on the SMs while they wait; good for one
+    // stream of back-to-back copies, bad here, where two lanes of every device must share the SMs (measured:
+    // 8.7 ms with it, 7.2 ms without at 4 GPUs).  Off for the launches of this call.
+    struct PdlOff {
+        int saved = lcb_tune_get("pdl");
+        PdlOff() { lcb_tune("pdl", 0); }
+        ~PdlOff() { lcb_tune("pdl", saved); }
+    } pdl_off;
+    const size_t kPiece = parts > 1 ? ((size_t)piece_mib << 20) : ~(size_t)0;
+    std::vector<cudaEvent_t> to_destroy;
+    std::vector<cudaStream_t> push_lane(parts, nullptr);
+    if (parts > 1) {
+        for (int k = 0; k < parts; ++k) {
+            LibreCUstream sg = streams[owners[k]];
+            if (off[k + 1] == off[k]) continue;
+            LIBRECUDA_ERR_PROPAGATE(bind(sg->ctx));
+            if (sg->side[0] == nullptr) {
+                LCU_CUDA(cudaStreamCreateWithFlags(&sg->side[0], cudaStreamNonBlocking));
+                LCU_CUDA(cudaEventCreateWithFlags(&sg->side_done[0], cudaEventDisableTiming));
+            }
+            push_lane[k] = sg->side[0];
+            LCU_CUDA(cudaEventRecord(sg->fork, sg->main));  // the push lane starts where the stream stands now
+            LCU_CUDA(cudaStreamWaitEvent(push_lane[k], sg->fork, 0));
+            sg->side_dirty[0] = true;  // joined into the main stream below
         }
     }
-    for (cudaEvent_t e : landed)
-        if (e) (void)cudaEventDestroy(e);
+    // pieces outermost, devices innermost: every device gets its first work within microseconds of the call
+    bool more = true;
+    for (size_t piece = 0; more; ++piece) {
+        more = false;
+        for (int k = 0; k < parts; ++k) {
+            const size_t shard = off[k + 1] - off[k];
+            if (kPiece != ~(size_t)0 ? piece * kPiece >= shard : piece > 0 || shard == 0) continue;
+            const size_t p = off[k] + (kPiece != ~(size_t)0 ? piece * kPiece : 0);
+            const size_t n = (kPiece == ~(size_t)0 || off[k + 1] - p < kPiece) ? off[k + 1] - p : kPiece;
+            if (p + n < off[k + 1]) more = true;
+            const int g = owners[k];
+            LibreCUstream sg = streams[g];
+            LIBRECUDA_ERR_PROPAGATE(bind(sg->ctx));
+            uint8_t *mine = static_cast<uint8_t *>(bufs[g]);
+            // The pull shares the root's port with all the other devices, so it is slow by construction; with a
+            // full grid its waiting CTAs would fill every SM and starve the forwarding kernels of this device
+            // (measured: the broadcast took twice as long).  74 looping CTAs carry the pull's share comfortably.
+            if (push_lane[k] == nullptr) LCU_LCB(lcb_copy_d2d(mine + p, src + p, n, sg->main));
+            else LCU_LCB(lcb_copy_d2d_ex(mine + p, src + p, n, LCB_COPY_VEC, pull_ctas, sg->main));
+            if (push_lane[k] == nullptr) continue;
+            cudaEvent_t landed;
+            LCU_CUDA(cudaEventCreateWithFlags(&landed, cudaEventDisableTiming));
+            to_destroy.push_back(landed);
+            LCU_CUDA(cudaEventRecord(landed, sg->main));
+            LCU_CUDA(cudaStreamWaitEvent(push_lane[k], landed, 0));
+            for (int step = 1; step < parts; ++step) {  // rotate the targets so the stores spread over the peers
+                const int q = owners[(k + step) % parts];
+                LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[q]) + p, mine + p, n, push_lane[k]));
+            }
+        }
+    }
+    for (int k = 0; k < parts; ++k) {
+        LibreCUstream sg = streams[owners[k]];
+        if (!sg->side_dirty[0]) continue;
+        LIBRECUDA_ERR_PROPAGATE(bind(sg->ctx));
+        LCU_CUDA(cudaEventRecord(sg->side_done[0], sg->side[0]));
+        LCU_CUDA(cudaStreamWaitEvent(sg->main, sg->side_done[0], 0));
+        sg->side_dirty[0] = false;
+    }
+    for (cudaEvent_t e : to_destroy) (void)cudaEventDestroy(e);
     LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
     return rebind_current();
 }

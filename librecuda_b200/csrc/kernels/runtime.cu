@@ -40,6 +40,8 @@ static const Tuning kDefaults = {
         /*tma2_depth*/ 2,
         /*tma2_stages*/ 8,
         /*tma2_chunk*/ 8192,
+        /*bcast_piece_mib*/ 64,
+        /*bcast_pull_ctas*/ 74,
 };
 
 Tuning &tuning() {
@@ -119,8 +121,24 @@ extern "C" int lcb_tune(const char *name, int value) {
     LCB_KNOB(tma2_depth)
     LCB_KNOB(tma2_stages)
     LCB_KNOB(tma2_chunk)
+    LCB_KNOB(bcast_piece_mib)
+    LCB_KNOB(bcast_pull_ctas)
 #undef LCB_KNOB
     return 1;
+}
+
+extern "C" int lcb_tune_get(const char *name) {
+    using lcb::tuning;
+    if (name == nullptr) return -1;
+#define LCB_KNOB(field) \
+    if (std::strcmp(name, #field) == 0) return tuning().field;
+    LCB_KNOB(bcast_piece_mib)
+    LCB_KNOB(bcast_pull_ctas)
+    LCB_KNOB(a2a_ctas_sm)
+    LCB_KNOB(pdl)
+    LCB_KNOB(auto_tma_min_mib)
+#undef LCB_KNOB
+    return -1;
 }
 
 extern "C" int lcb_preload(void) {

@@ -4,6 +4,7 @@
     python -m librecuda_b200.profile_case memset [--bytes N] [--reps R] [--path auto|vec|bulk]
     python -m librecuda_b200.profile_case index_fill | axpb | checksum | alltoall_self
     python -m librecuda_b200.profile_case sweep  [--max-log2 33]     (timing table, not for a profiler)
+    python -m librecuda_b200.profile_case multigpu [--gpus G] [--bytes N]   (one process driving G GPUs)
 
 The default 256 MiB per buffer is larger than the 126 MB L2 (DRAM counters stay meaningful) and small
 enough for a multi-pass capture to finish in about a minute.  Prints the CUDA-event time per launch.
@@ -65,9 +66,57 @@ def sweep(max_log2: int):
     t.destroy()
 
 
+def multigpu(n_gpus: int, nbytes: int, reps: int):
+    """libreCuBroadcast and libreCuAllToAll, own kernels against NCCL, in ONE process with a context per GPU.
+    Host wall clock around Commence..Await of all streams (the operations take milliseconds); GB/s per GPU:
+    broadcast = bytes / time, all-to-all = (G-1) * chunk / time."""
+    import time
+
+    lib = api.lib
+    api.init()
+    G = min(n_gpus, api.device_count())
+    ctxs = [api.Context(i) for i in range(G)]
+    streams, bufs, send, recv = [], [], [], []
+    chunk = nbytes // G // 16 * 16
+    for c in ctxs:
+        c.set_current()
+        for peer in ctxs:
+            if peer is not c:
+                c.enable_peer_access(peer)
+        streams.append(api.Stream())
+        bufs.append(api.DeviceBuffer(nbytes))
+        send.append(api.DeviceBuffer(G * chunk))
+        recv.append(api.DeviceBuffer(G * chunk))
+        api.lcb_check(lib.lcb_fill_splitmix64(send[-1].ptr, G * chunk, 40 + len(send), streams[-1].native), "fill")
+        streams[-1].run()
+    ctxs[0].set_current()
+    arr = lambda xs: (C.c_void_p * G)(*xs)
+    bp, sp, rp = arr([b.ptr for b in bufs]), arr([b.ptr for b in send]), arr([b.ptr for b in recv])
+    stp = arr([s.handle for s in streams])
+
+    def timed(fn):
+        best = 1e30
+        for i in range(reps + 2):
+            t0 = time.perf_counter()
+            api.check(fn(), "collective")
+            for s in streams:
+                s.await_()
+            if i >= 2:
+                best = min(best, time.perf_counter() - t0)
+        return best
+
+    print(f"{G} GPUs, one process; broadcast {nbytes} bytes from device 0, all-to-all {chunk} bytes per pair")
+    for name, use_nccl in (("own kernels", 0), ("NCCL", 1)):
+        t = timed(lambda: lib.libreCuBroadcast(bp, 0, nbytes, G, stp, use_nccl))
+        print(f"broadcast  {name:12s} {t * 1e3:8.3f} ms  {nbytes / t / 1e9:7.1f} GB/s")
+        t = timed(lambda: lib.libreCuAllToAll(rp, sp, chunk, G, stp, use_nccl))
+        print(f"all-to-all {name:12s} {t * 1e3:8.3f} ms  {(G - 1) * chunk / t / 1e9:7.1f} GB/s per GPU")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["copy", "memset", "index_fill", "axpb", "checksum", "alltoall_self", "sweep"])
+    ap.add_argument("kernel", choices=["copy", "memset", "index_fill", "axpb", "checksum", "alltoall_self", "sweep", "multigpu"])
+    ap.add_argument("--gpus", type=int, default=8)
     ap.add_argument("--max-log2", type=int, default=33)
     ap.add_argument("--bytes", type=int, default=256 << 20)
     ap.add_argument("--reps", type=int, default=3)
@@ -77,6 +126,8 @@ def main():
     args = ap.parse_args()
     if args.kernel == "sweep":
         return sweep(args.max_log2)
+    if args.kernel == "multigpu":
+        return multigpu(args.gpus, args.bytes if args.bytes != (256 << 20) else (4 << 30), max(args.reps, 5))
     lib = api.lib
     api.Context(0)
     st = api.Stream()
