@@ -123,6 +123,22 @@ PtrClass classify(const void *p) {
     return (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) ? PtrClass::Device : PtrClass::Host;
 }
 
+int owner_device(const void *p) {
+    auto &allocs = globals().allocations;
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    auto it = allocs.upper_bound(a);
+    if (it != allocs.begin()) {
+        --it;
+        if (a < it->first + it->second.size) return it->second.mapped ? -1 : it->second.device;
+    }
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return -1;
+    }
+    return attr.type == cudaMemoryTypeDevice ? attr.device : -1;
+}
+
 }  // namespace lcu
 
 using namespace lcu;

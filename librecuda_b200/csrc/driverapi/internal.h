@@ -102,6 +102,9 @@ enum class PtrClass { Host, Device };
 // classification used for the direction dispatch of libreCuMemCpy (reference: isDevicePtr,
 // driverapi/src/librecuda.cpp:821-836): library allocations first, then whatever the CUDA driver knows
 PtrClass classify(const void *p);
+// Device ordinal that owns a device pointer, or -1 when every device can reach it (managed memory) or the
+// owner is unknown to both the library and the CUDA driver.
+int owner_device(const void *p);
 
 }  // namespace lcu
 

@@ -392,6 +392,13 @@ libreCudaStatus_t libreCuIpcOpenMemHandle(void **pDevicePointer, const void *han
     void *raw = nullptr;
     LCU_CUDA(cudaIpcOpenMemHandle(&raw, h, cudaIpcMemLazyEnablePeerAccess));
     void *p = static_cast<uint8_t *>(raw) + offset;
+    // opening with cudaIpcMemLazyEnablePeerAccess gave this context access to the exporting GPU's memory
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, raw) == cudaSuccess && attr.type == cudaMemoryTypeDevice) {
+        globals().current->peers.insert(attr.device);
+    } else {
+        (void)cudaGetLastError();
+    }
     // size unknown on this side: register the page that holds the pointer so classification sees device memory;
     // the CUDA driver answers for the rest of the range
     globals().allocations[reinterpret_cast<uintptr_t>(p)] = Allocation{raw, 4096, globals().current->device->ordinal, false, true};

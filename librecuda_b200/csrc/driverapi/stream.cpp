@@ -249,6 +249,12 @@ static libreCudaStatus_t record_copy(void *dst, const void *src, size_t n, Libre
     c.src = src;
     c.bytes = n;
     if (dc == PtrClass::Device && sc == PtrClass::Device) {
+        // the copy kernel runs on the stream's GPU: both buffers must be its own or a peer's it was given
+        // access to (libreCuCtxEnablePeerAccess); refusing here is what keeps a bad pointer from faulting the GPU
+        for (const void *p : {static_cast<const void *>(dst), src}) {
+            const int owner = owner_device(p);
+            LIBRECUDA_VALIDATE(owner < 0 || stream->ctx->peers.count(owner) != 0, LIBRECUDA_ERROR_INVALID_VALUE);
+        }
         c.kind = Command::CopyKernel;  // reference: memcpyD2D, memcopy.cpp:77
     } else {
         c.kind = Command::CopyEngine;  // reference: gpuMemcpy, cmdqueue.cpp:732
@@ -312,6 +318,10 @@ static libreCudaStatus_t record_memset(void *dst, unsigned int value, int elem, 
     LCU_ENSURE_CTX();
     LIBRECUDA_VALIDATE((reinterpret_cast<uintptr_t>(dst) & (uintptr_t)(elem - 1)) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
     LIBRECUDA_VALIDATE(classify(dst) == PtrClass::Device, LIBRECUDA_ERROR_INVALID_VALUE);
+    {
+        const int owner = owner_device(dst);  // same rule as for kernel copies
+        LIBRECUDA_VALIDATE(owner < 0 || stream->ctx->peers.count(owner) != 0, LIBRECUDA_ERROR_INVALID_VALUE);
+    }
     if (count == 0) LIBRECUDA_SUCCEED();
     Command c;
     c.kind = Command::Memset;

@@ -208,3 +208,27 @@ def test_broadcast(gpus, use_nccl, root):
         ctxs[g].set_current()
         bufs[g].free()
     ctxs[0].set_current()
+
+
+def test_kernel_copy_into_unreachable_peer_memory_is_refused_not_faulted(gpu_count, ctx):
+    # a copy kernel on one GPU touching another GPU's memory without peer access would fault the GPU; a context
+    # that was never given access through libreCuCtxEnablePeerAccess is refused at the API instead
+    if gpu_count < 2:
+        pytest.skip("needs >= 2 GPUs")
+    ctx.set_current()
+    near = api.DeviceBuffer(4096)          # device 0
+    fresh = api.Context(1)                 # a new context on device 1: no peer access recorded for it
+    far = api.DeviceBuffer(4096)           # device 1
+    st = api.Stream()                      # stream of the fresh context
+    assert lib.libreCuMemCpy(near.ptr, far.ptr, 4096, st.handle, False) == api.ERROR_INVALID_VALUE
+    assert lib.libreCuMemCpy(far.ptr, near.ptr, 4096, st.handle, False) == api.ERROR_INVALID_VALUE
+    assert lib.libreCuMemsetD8(near.ptr, 0, 4096, st.handle) == api.ERROR_INVALID_VALUE
+    assert lib.libreCuMemsetD8(far.ptr, 0, 4096, st.handle) == api.SUCCESS      # its own memory is fine
+    st.run()
+    fresh.enable_peer_access(ctx)          # now allowed
+    assert lib.libreCuMemCpy(near.ptr, far.ptr, 4096, st.handle, False) == api.SUCCESS
+    st.run()
+    st.destroy()
+    far.free()
+    ctx.set_current()
+    near.free()
