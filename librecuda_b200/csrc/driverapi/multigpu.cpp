@@ -91,6 +91,14 @@ static libreCudaStatus_t record_alltoall(bool pull, void *const *peerBufs, void 
         LIBRECUDA_VALIDATE(peerBufs[j] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
         LIBRECUDA_VALIDATE((reinterpret_cast<uintptr_t>(peerBufs[j]) & 15) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
     }
+    {   // every buffer must be reachable from the GPU that runs the kernel
+        const int own = owner_device(mine);
+        LIBRECUDA_VALIDATE(own < 0 || stream->ctx->peers.count(own) != 0, LIBRECUDA_ERROR_INVALID_VALUE);
+        for (int j = 0; j < nRanks; ++j) {
+            const int owner = owner_device(peerBufs[j]);
+            LIBRECUDA_VALIDATE(owner < 0 || stream->ctx->peers.count(owner) != 0, LIBRECUDA_ERROR_INVALID_VALUE);
+        }
+    }
     if (chunkBytes == 0) LIBRECUDA_SUCCEED();
     Command c;
     c.kind = pull ? Command::AllToAllPull : Command::AllToAllPush;
@@ -176,6 +184,17 @@ libreCudaStatus_t nccl_group_for(Nccl *n, const std::vector<int> &devs) {
     LIBRECUDA_SUCCEED();
 }
 
+// every buffer of a collective must be reachable from every participating GPU's context
+libreCudaStatus_t check_reachable(int nDev, const LibreCUstream *streams, void *const *bufs) {
+    for (int r = 0; r < nDev; ++r) {
+        for (int j = 0; j < nDev; ++j) {
+            const int owner = owner_device(bufs[j]);
+            LIBRECUDA_VALIDATE(owner < 0 || streams[r]->ctx->peers.count(owner) != 0, LIBRECUDA_ERROR_INVALID_VALUE);
+        }
+    }
+    LIBRECUDA_SUCCEED();
+}
+
 libreCudaStatus_t check_group(int nDev, const LibreCUstream *streams, std::vector<int> *devs) {
     LIBRECUDA_VALIDATE(streams != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
     LIBRECUDA_VALIDATE(nDev >= 1 && nDev <= 16, LIBRECUDA_ERROR_INVALID_VALUE);
@@ -223,6 +242,10 @@ libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, 
     std::vector<int> devs;
     LIBRECUDA_ERR_PROPAGATE(check_group(nDev, streams, &devs));
     for (int r = 0; r < nDev; ++r) LIBRECUDA_VALIDATE(recvBufs[r] != nullptr && sendBufs[r] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    if (!useNccl) {
+        LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, recvBufs));
+        LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, sendBufs));
+    }
     for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(commence(streams[r]));
     if (chunkBytes == 0) LIBRECUDA_SUCCEED();
     if (useNccl) {
@@ -261,6 +284,7 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
     LIBRECUDA_ERR_PROPAGATE(check_group(nDev, streams, &devs));
     LIBRECUDA_VALIDATE(root >= 0 && root < nDev, LIBRECUDA_ERROR_INVALID_VALUE);
     for (int r = 0; r < nDev; ++r) LIBRECUDA_VALIDATE(bufs[r] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    if (!useNccl) LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, bufs));
     for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(commence(streams[r]));
     if (byteCount == 0 || nDev == 1) LIBRECUDA_SUCCEED();
     if (useNccl) {
