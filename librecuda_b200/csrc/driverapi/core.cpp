@@ -146,38 +146,40 @@ using namespace lcu;
 // ---- init / devices ---------------------------------------------------------------------------------------
 
 libreCudaStatus_t libreCuInit(int flags) {
-    (void)flags;
-    Globals &g = globals();
-    if (g.initialized) LIBRECUDA_SUCCEED();
-    int count = 0;
-    cudaError_t err = cudaGetDeviceCount(&count);
-    if (err != cudaSuccess || count <= 0) {
-        (void)cudaGetLastError();
-        LIBRECUDA_DEBUG("no usable CUDA device: " << (err != cudaSuccess ? cudaGetErrorName(err) : "device count 0"));
-        LIBRECUDA_FAIL(LIBRECUDA_ERROR_COMPAT_NOT_SUPPORTED_ON_DEVICE);
-    }
-    LIBRECUDA_VALIDATE(driver() != nullptr, LIBRECUDA_ERROR_COMPAT_NOT_SUPPORTED_ON_DEVICE);
-    for (int i = 0; i < count; ++i) {
-        auto d = std::make_unique<LibreCUdevice_>();
-        d->ordinal = i;
-        cudaDeviceProp prop{};
-        LCU_CUDA(cudaGetDeviceProperties(&prop, i));
-        d->name = prop.name;
-        d->cc_major = prop.major;
-        d->cc_minor = prop.minor;
-        d->smem_per_block = (int)prop.sharedMemPerBlock;
-        d->smem_optin = (int)prop.sharedMemPerBlockOptin;
-        d->max_block_x = prop.maxThreadsDim[0];
-        d->max_block_y = prop.maxThreadsDim[1];
-        d->max_block_z = prop.maxThreadsDim[2];
-        d->max_threads = prop.maxThreadsPerBlock;
-        d->max_grid_x = prop.maxGridSize[0];
-        d->max_grid_y = prop.maxGridSize[1];
-        d->max_grid_z = prop.maxGridSize[2];
-        g.devices.push_back(std::move(d));
-    }
-    g.initialized = true;
-    LIBRECUDA_SUCCEED();
+    return lcu_guarded([&]() -> libreCudaStatus_t {
+        (void)flags;
+        Globals &g = globals();
+        if (g.initialized) LIBRECUDA_SUCCEED();
+        int count = 0;
+        cudaError_t err = cudaGetDeviceCount(&count);
+        if (err != cudaSuccess || count <= 0) {
+            (void)cudaGetLastError();
+            LIBRECUDA_DEBUG("no usable CUDA device: " << (err != cudaSuccess ? cudaGetErrorName(err) : "device count 0"));
+            LIBRECUDA_FAIL(LIBRECUDA_ERROR_COMPAT_NOT_SUPPORTED_ON_DEVICE);
+        }
+        LIBRECUDA_VALIDATE(driver() != nullptr, LIBRECUDA_ERROR_COMPAT_NOT_SUPPORTED_ON_DEVICE);
+        for (int i = 0; i < count; ++i) {
+            auto d = std::make_unique<LibreCUdevice_>();
+            d->ordinal = i;
+            cudaDeviceProp prop{};
+            LCU_CUDA(cudaGetDeviceProperties(&prop, i));
+            d->name = prop.name;
+            d->cc_major = prop.major;
+            d->cc_minor = prop.minor;
+            d->smem_per_block = (int)prop.sharedMemPerBlock;
+            d->smem_optin = (int)prop.sharedMemPerBlockOptin;
+            d->max_block_x = prop.maxThreadsDim[0];
+            d->max_block_y = prop.maxThreadsDim[1];
+            d->max_block_z = prop.maxThreadsDim[2];
+            d->max_threads = prop.maxThreadsPerBlock;
+            d->max_grid_x = prop.maxGridSize[0];
+            d->max_grid_y = prop.maxGridSize[1];
+            d->max_grid_z = prop.maxGridSize[2];
+            g.devices.push_back(std::move(d));
+        }
+        g.initialized = true;
+        LIBRECUDA_SUCCEED();
+    });
 }
 
 libreCudaStatus_t libreCuDeviceGetCount(int *pDeviceCount) {
@@ -227,21 +229,23 @@ libreCudaStatus_t libreCuDeviceGetAttribute(int *pValOut, LibreCuDeviceAttribute
 // ---- contexts ----------------------------------------------------------------------------------------------
 
 libreCudaStatus_t libreCuCtxCreate_v2(LibreCUcontext *pCtx, int flags, LibreCUdevice device) {
-    LIBRECUDA_VALIDATE(pCtx != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    LIBRECUDA_VALIDATE(device != nullptr, LIBRECUDA_ERROR_INVALID_DEVICE);
-    LCU_ENSURE_INIT();
-    auto ctx = std::make_unique<LibreCUcontext_>();
-    ctx->device = device;
-    ctx->flags = flags;
-    ctx->peers.insert(device->ordinal);
-    LCU_CUDA(cudaSetDevice(device->ordinal));
-    LCU_CUDA(cudaFree(nullptr));  // forces creation of the primary context
-    LCU_CUDA(cudaEventCreate(&ctx->epoch));
-    LCU_CUDA(cudaEventRecord(ctx->epoch, nullptr));
-    LCU_LCB(lcb_preload());  // the reference loads its copy kernels here as well (librecuda.cpp:622)
-    globals().current = ctx.get();  // reference: librecuda.cpp:619
-    *pCtx = ctx.release();
-    LIBRECUDA_SUCCEED();
+    return lcu_guarded([&]() -> libreCudaStatus_t {
+        LIBRECUDA_VALIDATE(pCtx != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(device != nullptr, LIBRECUDA_ERROR_INVALID_DEVICE);
+        LCU_ENSURE_INIT();
+        auto ctx = std::make_unique<LibreCUcontext_>();
+        ctx->device = device;
+        ctx->flags = flags;
+        ctx->peers.insert(device->ordinal);
+        LCU_CUDA(cudaSetDevice(device->ordinal));
+        LCU_CUDA(cudaFree(nullptr));  // forces creation of the primary context
+        LCU_CUDA(cudaEventCreate(&ctx->epoch));
+        LCU_CUDA(cudaEventRecord(ctx->epoch, nullptr));
+        LCU_LCB(lcb_preload());  // the reference loads its copy kernels here as well (librecuda.cpp:622)
+        globals().current = ctx.get();  // reference: librecuda.cpp:619
+        *pCtx = ctx.release();
+        LIBRECUDA_SUCCEED();
+    });
 }
 
 libreCudaStatus_t libreCuCtxDestroy(LibreCUcontext ctx) {
@@ -272,29 +276,31 @@ libreCudaStatus_t libreCuCtxGetCurrent(LibreCUcontext *pCtxOut) {
 // ---- memory ---------------------------------------------------------------------------------------------------
 
 libreCudaStatus_t libreCuMemAlloc(void **pDevicePointer, size_t bytesize, bool mapToCpu) {
-    LIBRECUDA_VALIDATE(pDevicePointer != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    LIBRECUDA_VALIDATE(bytesize != 0, LIBRECUDA_ERROR_INVALID_VALUE);
-    LCU_ENSURE_CTX();
-    Globals &g = globals();
-    LIBRECUDA_ERR_PROPAGATE(bind(g.current));
-    // the reference rounds to 4 KiB pages (2 MiB above 16 MiB) and returns page-aligned addresses
-    // (librecuda.cpp:694-695,743); keep the 4 KiB alignment guarantee
-    constexpr size_t kPage = 4096;
-    const size_t rounded = (bytesize + kPage - 1) / kPage * kPage;
-    void *raw = nullptr;
-    auto alloc = [&](size_t n) -> cudaError_t {
-        return mapToCpu ? cudaMallocManaged(&raw, n, cudaMemAttachGlobal) : cudaMalloc(&raw, n);
-    };
-    LCU_CUDA(alloc(rounded));
-    void *aligned = raw;
-    if (reinterpret_cast<uintptr_t>(raw) % kPage) {
-        LCU_CUDA(cudaFree(raw));
-        LCU_CUDA(alloc(rounded + kPage));
-        aligned = reinterpret_cast<void *>((reinterpret_cast<uintptr_t>(raw) + kPage - 1) / kPage * kPage);
-    }
-    g.allocations[reinterpret_cast<uintptr_t>(aligned)] = Allocation{raw, rounded, g.current->device->ordinal, mapToCpu, false};
-    *pDevicePointer = aligned;
-    LIBRECUDA_SUCCEED();
+    return lcu_guarded([&]() -> libreCudaStatus_t {
+        LIBRECUDA_VALIDATE(pDevicePointer != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(bytesize != 0, LIBRECUDA_ERROR_INVALID_VALUE);
+        LCU_ENSURE_CTX();
+        Globals &g = globals();
+        LIBRECUDA_ERR_PROPAGATE(bind(g.current));
+        // the reference rounds to 4 KiB pages (2 MiB above 16 MiB) and returns page-aligned addresses
+        // (librecuda.cpp:694-695,743); keep the 4 KiB alignment guarantee
+        constexpr size_t kPage = 4096;
+        const size_t rounded = (bytesize + kPage - 1) / kPage * kPage;
+        void *raw = nullptr;
+        auto alloc = [&](size_t n) -> cudaError_t {
+            return mapToCpu ? cudaMallocManaged(&raw, n, cudaMemAttachGlobal) : cudaMalloc(&raw, n);
+        };
+        LCU_CUDA(alloc(rounded));
+        void *aligned = raw;
+        if (reinterpret_cast<uintptr_t>(raw) % kPage) {
+            LCU_CUDA(cudaFree(raw));
+            LCU_CUDA(alloc(rounded + kPage));
+            aligned = reinterpret_cast<void *>((reinterpret_cast<uintptr_t>(raw) + kPage - 1) / kPage * kPage);
+        }
+        g.allocations[reinterpret_cast<uintptr_t>(aligned)] = Allocation{raw, rounded, g.current->device->ordinal, mapToCpu, false};
+        *pDevicePointer = aligned;
+        LIBRECUDA_SUCCEED();
+    });
 }
 
 libreCudaStatus_t libreCuMemFree(void *devicePointer) {

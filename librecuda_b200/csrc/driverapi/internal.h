@@ -11,6 +11,7 @@
 #include <cstdint>
 #include <map>
 #include <memory>
+#include <new>
 #include <set>
 #include <string>
 #include <vector>
@@ -208,6 +209,19 @@ libreCudaStatus_t staged_h2d(LibreCUstream st, cudaStream_t lane, void *dst, con
 libreCudaStatus_t staged_d2h(LibreCUstream st, cudaStream_t lane, void *dst, const void *src, size_t bytes);
 void free_ring(LibreCUstream st);
 }  // namespace lcu
+
+// No C++ exception may cross the C ABI (the reference lets one escape, cmdqueue.cpp:353-355): entry points that
+// allocate run their body through this guard.
+template <typename Fn>
+inline libreCudaStatus_t lcu_guarded(Fn &&body) {
+    try {
+        return body();
+    } catch (const std::bad_alloc &) {
+        return LIBRECUDA_ERROR_OUT_OF_MEMORY;
+    } catch (...) {
+        return LIBRECUDA_ERROR_UNKNOWN;
+    }
+}
 
 #define LCU_ENSURE_INIT() LIBRECUDA_VALIDATE(lcu::globals().initialized, LIBRECUDA_ERROR_NOT_INITIALIZED)
 #define LCU_ENSURE_CTX() LIBRECUDA_VALIDATE(lcu::globals().current != nullptr, LIBRECUDA_ERROR_INVALID_CONTEXT)

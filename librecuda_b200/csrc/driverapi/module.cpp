@@ -35,34 +35,36 @@ static libreCudaStatus_t describe(LibreCUFunction f) {
 }
 
 libreCudaStatus_t libreCuModuleLoadData(LibreCUmodule *pModuleOut, const void *image, size_t imageSize) {
-    LIBRECUDA_VALIDATE(pModuleOut != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    LIBRECUDA_VALIDATE(image != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    LIBRECUDA_VALIDATE(imageSize >= 4, LIBRECUDA_ERROR_INVALID_IMAGE);
-    LCU_ENSURE_CTX();
-    const DriverTable *drv = driver();
-    LIBRECUDA_VALIDATE(drv != nullptr, LIBRECUDA_ERROR_NOT_INITIALIZED);
-    LibreCUcontext ctx = globals().current;
-    LIBRECUDA_ERR_PROPAGATE(bind(ctx));
-    auto mod = std::make_unique<LibreCUmodule_>();
-    mod->ctx = ctx;
-    CUresult res = drv->ModuleLoadData(&mod->mod, image);
-    if (res != CUDA_SUCCESS) {
-        LIBRECUDA_DEBUG("cuModuleLoadData failed: CUresult " << (int)res);
-        LIBRECUDA_FAIL(res == CUDA_ERROR_OUT_OF_MEMORY ? LIBRECUDA_ERROR_OUT_OF_MEMORY : LIBRECUDA_ERROR_INVALID_IMAGE);
-    }
-    unsigned int count = 0;
-    LCU_CU(drv->ModuleGetFunctionCount(&count, mod->mod));
-    std::vector<CUfunction> fns(count);
-    if (count) LCU_CU(drv->ModuleEnumerateFunctions(fns.data(), count, mod->mod));
-    for (CUfunction fn : fns) {
-        auto f = std::make_unique<LibreCUFunction_>();
-        f->module = mod.get();
-        f->fn = fn;
-        LIBRECUDA_ERR_PROPAGATE(describe(f.get()));
-        mod->functions.push_back(std::move(f));
-    }
-    *pModuleOut = mod.release();
-    LIBRECUDA_SUCCEED();
+    return lcu_guarded([&]() -> libreCudaStatus_t {
+        LIBRECUDA_VALIDATE(pModuleOut != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(image != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(imageSize >= 4, LIBRECUDA_ERROR_INVALID_IMAGE);
+        LCU_ENSURE_CTX();
+        const DriverTable *drv = driver();
+        LIBRECUDA_VALIDATE(drv != nullptr, LIBRECUDA_ERROR_NOT_INITIALIZED);
+        LibreCUcontext ctx = globals().current;
+        LIBRECUDA_ERR_PROPAGATE(bind(ctx));
+        auto mod = std::make_unique<LibreCUmodule_>();
+        mod->ctx = ctx;
+        CUresult res = drv->ModuleLoadData(&mod->mod, image);
+        if (res != CUDA_SUCCESS) {
+            LIBRECUDA_DEBUG("cuModuleLoadData failed: CUresult " << (int)res);
+            LIBRECUDA_FAIL(res == CUDA_ERROR_OUT_OF_MEMORY ? LIBRECUDA_ERROR_OUT_OF_MEMORY : LIBRECUDA_ERROR_INVALID_IMAGE);
+        }
+        unsigned int count = 0;
+        LCU_CU(drv->ModuleGetFunctionCount(&count, mod->mod));
+        std::vector<CUfunction> fns(count);
+        if (count) LCU_CU(drv->ModuleEnumerateFunctions(fns.data(), count, mod->mod));
+        for (CUfunction fn : fns) {
+            auto f = std::make_unique<LibreCUFunction_>();
+            f->module = mod.get();
+            f->fn = fn;
+            LIBRECUDA_ERR_PROPAGATE(describe(f.get()));
+            mod->functions.push_back(std::move(f));
+        }
+        *pModuleOut = mod.release();
+        LIBRECUDA_SUCCEED();
+    });
 }
 
 libreCudaStatus_t libreCuModuleUnload(LibreCUmodule module) {
@@ -128,34 +130,36 @@ libreCudaStatus_t libreCuFuncSetAttribute(LibreCUFunction function, LibreCuFunct
 libreCudaStatus_t libreCuLaunchKernel(LibreCUFunction function, uint32_t gridDimX, uint32_t gridDimY, uint32_t gridDimZ,
                                       uint32_t blockDimX, uint32_t blockDimY, uint32_t blockDimZ, uint32_t sharedMemBytes,
                                       LibreCUstream stream, void **kernelParams, size_t numParams, void **extra, bool async) {
-    (void)extra;
-    LIBRECUDA_VALIDATE(function != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    LCU_ENSURE_CTX();
-    LIBRECUDA_VALIDATE(numParams == function->param_size.size(), LIBRECUDA_ERROR_INVALID_VALUE);  // reference cmdqueue.cpp:467
-    LIBRECUDA_VALIDATE(numParams == 0 || kernelParams != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    const LibreCUdevice dev = stream->ctx->device;
-    // launch limits of the device (the reference hard-codes them, cmdqueue.cpp:592-598)
-    LIBRECUDA_VALIDATE(blockDimX >= 1 && blockDimX <= (uint32_t)dev->max_block_x, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
-    LIBRECUDA_VALIDATE(blockDimY >= 1 && blockDimY <= (uint32_t)dev->max_block_y, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
-    LIBRECUDA_VALIDATE(blockDimZ >= 1 && blockDimZ <= (uint32_t)dev->max_block_z, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
-    LIBRECUDA_VALIDATE((uint64_t)blockDimX * blockDimY * blockDimZ <= (uint64_t)dev->max_threads, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
-    LIBRECUDA_VALIDATE(gridDimX >= 1 && gridDimX <= (uint32_t)dev->max_grid_x, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
-    LIBRECUDA_VALIDATE(gridDimY >= 1 && gridDimY <= (uint32_t)dev->max_grid_y, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
-    LIBRECUDA_VALIDATE(gridDimZ >= 1 && gridDimZ <= (uint32_t)dev->max_grid_z, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
-    Command c;
-    c.kind = Command::Launch;
-    c.async = async;
-    c.fn = function;
-    c.grid[0] = gridDimX; c.grid[1] = gridDimY; c.grid[2] = gridDimZ;
-    c.block[0] = blockDimX; c.block[1] = blockDimY; c.block[2] = blockDimZ;
-    // shared memory = max(value set through libreCuFuncSetAttribute, sharedMemBytes), reference cmdqueue.cpp:585
-    c.smem = sharedMemBytes > (uint32_t)function->dyn_smem_attr ? sharedMemBytes : (uint32_t)function->dyn_smem_attr;
-    LIBRECUDA_VALIDATE(c.smem <= (uint32_t)dev->smem_optin, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
-    c.params.assign(function->param_bytes, 0);
-    for (size_t i = 0; i < numParams; ++i) {
-        LIBRECUDA_VALIDATE(kernelParams[i] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-        std::memcpy(c.params.data() + function->param_offset[i], kernelParams[i], function->param_size[i]);
-    }
-    return record(stream, std::move(c));
+    return lcu_guarded([&]() -> libreCudaStatus_t {
+        (void)extra;
+        LIBRECUDA_VALIDATE(function != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LCU_ENSURE_CTX();
+        LIBRECUDA_VALIDATE(numParams == function->param_size.size(), LIBRECUDA_ERROR_INVALID_VALUE);  // reference cmdqueue.cpp:467
+        LIBRECUDA_VALIDATE(numParams == 0 || kernelParams != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        const LibreCUdevice dev = stream->ctx->device;
+        // launch limits of the device (the reference hard-codes them, cmdqueue.cpp:592-598)
+        LIBRECUDA_VALIDATE(blockDimX >= 1 && blockDimX <= (uint32_t)dev->max_block_x, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
+        LIBRECUDA_VALIDATE(blockDimY >= 1 && blockDimY <= (uint32_t)dev->max_block_y, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
+        LIBRECUDA_VALIDATE(blockDimZ >= 1 && blockDimZ <= (uint32_t)dev->max_block_z, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
+        LIBRECUDA_VALIDATE((uint64_t)blockDimX * blockDimY * blockDimZ <= (uint64_t)dev->max_threads, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
+        LIBRECUDA_VALIDATE(gridDimX >= 1 && gridDimX <= (uint32_t)dev->max_grid_x, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
+        LIBRECUDA_VALIDATE(gridDimY >= 1 && gridDimY <= (uint32_t)dev->max_grid_y, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
+        LIBRECUDA_VALIDATE(gridDimZ >= 1 && gridDimZ <= (uint32_t)dev->max_grid_z, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
+        Command c;
+        c.kind = Command::Launch;
+        c.async = async;
+        c.fn = function;
+        c.grid[0] = gridDimX; c.grid[1] = gridDimY; c.grid[2] = gridDimZ;
+        c.block[0] = blockDimX; c.block[1] = blockDimY; c.block[2] = blockDimZ;
+        // shared memory = max(value set through libreCuFuncSetAttribute, sharedMemBytes), reference cmdqueue.cpp:585
+        c.smem = sharedMemBytes > (uint32_t)function->dyn_smem_attr ? sharedMemBytes : (uint32_t)function->dyn_smem_attr;
+        LIBRECUDA_VALIDATE(c.smem <= (uint32_t)dev->smem_optin, LIBRECUDA_ERROR_LAUNCH_OUT_OF_RESOURCES);
+        c.params.assign(function->param_bytes, 0);
+        for (size_t i = 0; i < numParams; ++i) {
+            LIBRECUDA_VALIDATE(kernelParams[i] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+            std::memcpy(c.params.data() + function->param_offset[i], kernelParams[i], function->param_size[i]);
+        }
+        return record(stream, std::move(c));
+    });
 }

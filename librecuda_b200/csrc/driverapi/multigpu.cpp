@@ -64,19 +64,21 @@ libreCudaStatus_t libreCuPartitionPlan(size_t totalBytes, int parts, size_t alig
 
 libreCudaStatus_t libreCuMemcpyPartitioned(void *const *dsts, const void *src, size_t totalBytes, int parts,
                                            size_t alignBytes, const LibreCUstream *streams) {
-    LIBRECUDA_VALIDATE(dsts != nullptr && src != nullptr && streams != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    LIBRECUDA_VALIDATE(parts >= 1 && parts <= 64, LIBRECUDA_ERROR_INVALID_VALUE);
-    size_t off[65];
-    LIBRECUDA_ERR_PROPAGATE(libreCuPartitionPlan(totalBytes, parts, alignBytes, off));
-    for (int g = 0; g < parts; ++g) {
-        LIBRECUDA_VALIDATE(dsts[g] != nullptr && streams[g] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    }
-    for (int g = 0; g < parts; ++g) {
-        if (off[g + 1] == off[g]) continue;
-        LIBRECUDA_ERR_PROPAGATE(libreCuMemcpyPeer(dsts[g], static_cast<const uint8_t *>(src) + off[g], off[g + 1] - off[g],
-                                                  streams[g], false));
-    }
-    LIBRECUDA_SUCCEED();
+    return lcu_guarded([&]() -> libreCudaStatus_t {
+        LIBRECUDA_VALIDATE(dsts != nullptr && src != nullptr && streams != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(parts >= 1 && parts <= 64, LIBRECUDA_ERROR_INVALID_VALUE);
+        size_t off[65];
+        LIBRECUDA_ERR_PROPAGATE(libreCuPartitionPlan(totalBytes, parts, alignBytes, off));
+        for (int g = 0; g < parts; ++g) {
+            LIBRECUDA_VALIDATE(dsts[g] != nullptr && streams[g] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        }
+        for (int g = 0; g < parts; ++g) {
+            if (off[g + 1] == off[g]) continue;
+            LIBRECUDA_ERR_PROPAGATE(libreCuMemcpyPeer(dsts[g], static_cast<const uint8_t *>(src) + off[g], off[g + 1] - off[g],
+                                                      streams[g], false));
+        }
+        LIBRECUDA_SUCCEED();
+    });
 }
 
 // ---- all-to-all ---------------------------------------------------------------------------------------------
@@ -238,151 +240,155 @@ libreCudaStatus_t rebind_current() {
 // libreCuStreamAwait on the participating streams.
 libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, size_t chunkBytes, int nDev,
                                   const LibreCUstream *streams, int useNccl) {
-    LIBRECUDA_VALIDATE(recvBufs != nullptr && sendBufs != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    std::vector<int> devs;
-    LIBRECUDA_ERR_PROPAGATE(check_group(nDev, streams, &devs));
-    for (int r = 0; r < nDev; ++r) LIBRECUDA_VALIDATE(recvBufs[r] != nullptr && sendBufs[r] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    if (!useNccl) {
-        LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, recvBufs));
-        LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, sendBufs));
-    }
-    for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(commence(streams[r]));
-    if (chunkBytes == 0) LIBRECUDA_SUCCEED();
-    if (useNccl) {
-        Nccl *n = nccl();
-        LIBRECUDA_VALIDATE(n != nullptr, LIBRECUDA_ERROR_NOT_FOUND);
-        LIBRECUDA_ERR_PROPAGATE(nccl_group_for(n, devs));
-        LCU_NCCL(n, n->GroupStart());
-        for (int r = 0; r < nDev; ++r) {
-            const uint8_t *s = static_cast<const uint8_t *>(sendBufs[r]);
-            uint8_t *d = static_cast<uint8_t *>(recvBufs[r]);
-            for (int j = 0; j < nDev; ++j) {
-                LCU_NCCL(n, n->Send(s + (size_t)j * chunkBytes, chunkBytes, ncclUint8, j, n->comms[r], streams[r]->main));
-                LCU_NCCL(n, n->Recv(d + (size_t)j * chunkBytes, chunkBytes, ncclUint8, j, n->comms[r], streams[r]->main));
+    return lcu_guarded([&]() -> libreCudaStatus_t {
+        LIBRECUDA_VALIDATE(recvBufs != nullptr && sendBufs != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        std::vector<int> devs;
+        LIBRECUDA_ERR_PROPAGATE(check_group(nDev, streams, &devs));
+        for (int r = 0; r < nDev; ++r) LIBRECUDA_VALIDATE(recvBufs[r] != nullptr && sendBufs[r] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        if (!useNccl) {
+            LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, recvBufs));
+            LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, sendBufs));
+        }
+        for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(commence(streams[r]));
+        if (chunkBytes == 0) LIBRECUDA_SUCCEED();
+        if (useNccl) {
+            Nccl *n = nccl();
+            LIBRECUDA_VALIDATE(n != nullptr, LIBRECUDA_ERROR_NOT_FOUND);
+            LIBRECUDA_ERR_PROPAGATE(nccl_group_for(n, devs));
+            LCU_NCCL(n, n->GroupStart());
+            for (int r = 0; r < nDev; ++r) {
+                const uint8_t *s = static_cast<const uint8_t *>(sendBufs[r]);
+                uint8_t *d = static_cast<uint8_t *>(recvBufs[r]);
+                for (int j = 0; j < nDev; ++j) {
+                    LCU_NCCL(n, n->Send(s + (size_t)j * chunkBytes, chunkBytes, ncclUint8, j, n->comms[r], streams[r]->main));
+                    LCU_NCCL(n, n->Recv(d + (size_t)j * chunkBytes, chunkBytes, ncclUint8, j, n->comms[r], streams[r]->main));
+                }
             }
+            LCU_NCCL(n, n->GroupEnd());
+        } else {
+            LIBRECUDA_VALIDATE((chunkBytes & 15) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
+            // rank r must not overwrite a receive slot its peer may still be using: start after everything
+            // submitted so far on every stream.  Stores, not loads: with every link busy in both directions remote
+            // stores are the faster form (704 vs 665 GB/s per GPU measured).
+            LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+            for (int r = 0; r < nDev; ++r) {
+                LIBRECUDA_ERR_PROPAGATE(bind(streams[r]->ctx));
+                LCU_LCB(lcb_alltoall_push(recvBufs, sendBufs[r], chunkBytes, nDev, r, streams[r]->main));
+            }
+            LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
         }
-        LCU_NCCL(n, n->GroupEnd());
-    } else {
-        LIBRECUDA_VALIDATE((chunkBytes & 15) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
-        // rank r must not overwrite a receive slot its peer may still be using: start after everything
-        // submitted so far on every stream.  Stores, not loads: with every link busy in both directions remote
-        // stores are the faster form (704 vs 665 GB/s per GPU measured).
-        LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
-        for (int r = 0; r < nDev; ++r) {
-            LIBRECUDA_ERR_PROPAGATE(bind(streams[r]->ctx));
-            LCU_LCB(lcb_alltoall_push(recvBufs, sendBufs[r], chunkBytes, nDev, r, streams[r]->main));
-        }
-        LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
-    }
-    return rebind_current();
+        return rebind_current();
+    });
 }
 
 libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount, int nDev, const LibreCUstream *streams,
                                    int useNccl) {
-    LIBRECUDA_VALIDATE(bufs != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    std::vector<int> devs;
-    LIBRECUDA_ERR_PROPAGATE(check_group(nDev, streams, &devs));
-    LIBRECUDA_VALIDATE(root >= 0 && root < nDev, LIBRECUDA_ERROR_INVALID_VALUE);
-    for (int r = 0; r < nDev; ++r) LIBRECUDA_VALIDATE(bufs[r] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    if (!useNccl) LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, bufs));
-    for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(commence(streams[r]));
-    if (byteCount == 0 || nDev == 1) LIBRECUDA_SUCCEED();
-    if (useNccl) {
-        Nccl *n = nccl();
-        LIBRECUDA_VALIDATE(n != nullptr, LIBRECUDA_ERROR_NOT_FOUND);
-        LIBRECUDA_ERR_PROPAGATE(nccl_group_for(n, devs));
-        LCU_NCCL(n, n->GroupStart());
-        for (int r = 0; r < nDev; ++r)
-            LCU_NCCL(n, n->Broadcast(bufs[root], bufs[r], byteCount, ncclUint8, root, n->comms[r], streams[r]->main));
-        LCU_NCCL(n, n->GroupEnd());
-        return rebind_current();
-    }
-    // Own path.  The buffer is cut into one shard per non-root device, each shard into pieces.
-    //   pull lane of device g : loads piece after piece of shard g from the root (every byte leaves the root
-    //                           exactly once; remote loads are the faster direction while the root only sends);
-    //   push lane of device g : as soon as a piece has landed, stores it to every other non-root device (with
-    //                           all those links busy in both directions, stores are the faster form).
-    // The two lanes are separate CUDA streams tied by one event per piece, so forwarding piece p overlaps the
-    // arrival of piece p+1 and the whole broadcast takes about one buffer's worth of link time.
-    std::vector<int> owners;
-    for (int g = 0; g < nDev; ++g)
-        if (g != root) owners.push_back(g);
-    const int parts = (int)owners.size();
-    size_t off[17];
-    LIBRECUDA_ERR_PROPAGATE(libreCuPartitionPlan(byteCount, parts, 0, off));
-    LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
-    const uint8_t *src = static_cast<const uint8_t *>(bufs[root]);
-    // one piece when there is nobody to forward to; otherwise pipelined pieces (64 MiB by default)
-    const int piece_mib = lcb_tune_get("bcast_piece_mib") > 0 ? lcb_tune_get("bcast_piece_mib") : 64;
-    const int pull_ctas = lcb_tune_get("bcast_pull_ctas") > 0 ? lcb_tune_get("bcast_pull_ctas") : 74;
-    // Programmatic dependent launch parks the next kernel's CTAs on the SMs while they wait; good for one
-    // stream of back-to-back copies, bad here, where two lanes of every device must share the SMs (measured:
-    // 8.7 ms with it, 7.2 ms without at 4 GPUs).  Off for the launches of this call.
-    struct PdlOff {
-        int saved = lcb_tune_get("pdl");
-        PdlOff() { lcb_tune("pdl", 0); }
-        ~PdlOff() { lcb_tune("pdl", saved); }
-    } pdl_off;
-    const size_t kPiece = parts > 1 ? ((size_t)piece_mib << 20) : ~(size_t)0;
-    std::vector<cudaEvent_t> to_destroy;
-    std::vector<cudaStream_t> push_lane(parts, nullptr);
-    if (parts > 1) {
+    return lcu_guarded([&]() -> libreCudaStatus_t {
+        LIBRECUDA_VALIDATE(bufs != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        std::vector<int> devs;
+        LIBRECUDA_ERR_PROPAGATE(check_group(nDev, streams, &devs));
+        LIBRECUDA_VALIDATE(root >= 0 && root < nDev, LIBRECUDA_ERROR_INVALID_VALUE);
+        for (int r = 0; r < nDev; ++r) LIBRECUDA_VALIDATE(bufs[r] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        if (!useNccl) LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, bufs));
+        for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(commence(streams[r]));
+        if (byteCount == 0 || nDev == 1) LIBRECUDA_SUCCEED();
+        if (useNccl) {
+            Nccl *n = nccl();
+            LIBRECUDA_VALIDATE(n != nullptr, LIBRECUDA_ERROR_NOT_FOUND);
+            LIBRECUDA_ERR_PROPAGATE(nccl_group_for(n, devs));
+            LCU_NCCL(n, n->GroupStart());
+            for (int r = 0; r < nDev; ++r)
+                LCU_NCCL(n, n->Broadcast(bufs[root], bufs[r], byteCount, ncclUint8, root, n->comms[r], streams[r]->main));
+            LCU_NCCL(n, n->GroupEnd());
+            return rebind_current();
+        }
+        // Own path.  The buffer is cut into one shard per non-root device, each shard into pieces.
+        //   pull lane of device g : loads piece after piece of shard g from the root (every byte leaves the root
+        //                           exactly once; remote loads are the faster direction while the root only sends);
+        //   push lane of device g : as soon as a piece has landed, stores it to every other non-root device (with
+        //                           all those links busy in both directions, stores are the faster form).
+        // The two lanes are separate CUDA streams tied by one event per piece, so forwarding piece p overlaps the
+        // arrival of piece p+1 and the whole broadcast takes about one buffer's worth of link time.
+        std::vector<int> owners;
+        for (int g = 0; g < nDev; ++g)
+            if (g != root) owners.push_back(g);
+        const int parts = (int)owners.size();
+        size_t off[17];
+        LIBRECUDA_ERR_PROPAGATE(libreCuPartitionPlan(byteCount, parts, 0, off));
+        LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+        const uint8_t *src = static_cast<const uint8_t *>(bufs[root]);
+        // one piece when there is nobody to forward to; otherwise pipelined pieces (64 MiB by default)
+        const int piece_mib = lcb_tune_get("bcast_piece_mib") > 0 ? lcb_tune_get("bcast_piece_mib") : 64;
+        const int pull_ctas = lcb_tune_get("bcast_pull_ctas") > 0 ? lcb_tune_get("bcast_pull_ctas") : 74;
+        // Programmatic dependent launch parks the next kernel's CTAs on the SMs while they wait; good for one
+        // stream of back-to-back copies, bad here, where two lanes of every device must share the SMs (measured:
+        // 8.7 ms with it, 7.2 ms without at 4 GPUs).  Off for the launches of this call.
+        struct PdlOff {
+            int saved = lcb_tune_get("pdl");
+            PdlOff() { lcb_tune("pdl", 0); }
+            ~PdlOff() { lcb_tune("pdl", saved); }
+        } pdl_off;
+        const size_t kPiece = parts > 1 ? ((size_t)piece_mib << 20) : ~(size_t)0;
+        std::vector<cudaEvent_t> to_destroy;
+        std::vector<cudaStream_t> push_lane(parts, nullptr);
+        if (parts > 1) {
+            for (int k = 0; k < parts; ++k) {
+                LibreCUstream sg = streams[owners[k]];
+                if (off[k + 1] == off[k]) continue;
+                LIBRECUDA_ERR_PROPAGATE(bind(sg->ctx));
+                if (sg->side[0] == nullptr) {
+                    LCU_CUDA(cudaStreamCreateWithFlags(&sg->side[0], cudaStreamNonBlocking));
+                    LCU_CUDA(cudaEventCreateWithFlags(&sg->side_done[0], cudaEventDisableTiming));
+                }
+                push_lane[k] = sg->side[0];
+                LCU_CUDA(cudaEventRecord(sg->fork, sg->main));  // the push lane starts where the stream stands now
+                LCU_CUDA(cudaStreamWaitEvent(push_lane[k], sg->fork, 0));
+                sg->side_dirty[0] = true;  // joined into the main stream below
+            }
+        }
+        // pieces outermost, devices innermost: every device gets its first work within microseconds of the call
+        bool more = true;
+        for (size_t piece = 0; more; ++piece) {
+            more = false;
+            for (int k = 0; k < parts; ++k) {
+                const size_t shard = off[k + 1] - off[k];
+                if (kPiece != ~(size_t)0 ? piece * kPiece >= shard : piece > 0 || shard == 0) continue;
+                const size_t p = off[k] + (kPiece != ~(size_t)0 ? piece * kPiece : 0);
+                const size_t n = (kPiece == ~(size_t)0 || off[k + 1] - p < kPiece) ? off[k + 1] - p : kPiece;
+                if (p + n < off[k + 1]) more = true;
+                const int g = owners[k];
+                LibreCUstream sg = streams[g];
+                LIBRECUDA_ERR_PROPAGATE(bind(sg->ctx));
+                uint8_t *mine = static_cast<uint8_t *>(bufs[g]);
+                // The pull shares the root's port with all the other devices, so it is slow by construction; with a
+                // full grid its waiting CTAs would fill every SM and starve the forwarding kernels of this device
+                // (measured: the broadcast took twice as long).  74 looping CTAs carry the pull's share comfortably.
+                if (push_lane[k] == nullptr) LCU_LCB(lcb_copy_d2d(mine + p, src + p, n, sg->main));
+                else LCU_LCB(lcb_copy_d2d_ex(mine + p, src + p, n, LCB_COPY_VEC, pull_ctas, sg->main));
+                if (push_lane[k] == nullptr) continue;
+                cudaEvent_t landed;
+                LCU_CUDA(cudaEventCreateWithFlags(&landed, cudaEventDisableTiming));
+                to_destroy.push_back(landed);
+                LCU_CUDA(cudaEventRecord(landed, sg->main));
+                LCU_CUDA(cudaStreamWaitEvent(push_lane[k], landed, 0));
+                for (int step = 1; step < parts; ++step) {  // rotate the targets so the stores spread over the peers
+                    const int q = owners[(k + step) % parts];
+                    LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[q]) + p, mine + p, n, push_lane[k]));
+                }
+            }
+        }
         for (int k = 0; k < parts; ++k) {
             LibreCUstream sg = streams[owners[k]];
-            if (off[k + 1] == off[k]) continue;
+            if (!sg->side_dirty[0]) continue;
             LIBRECUDA_ERR_PROPAGATE(bind(sg->ctx));
-            if (sg->side[0] == nullptr) {
-                LCU_CUDA(cudaStreamCreateWithFlags(&sg->side[0], cudaStreamNonBlocking));
-                LCU_CUDA(cudaEventCreateWithFlags(&sg->side_done[0], cudaEventDisableTiming));
-            }
-            push_lane[k] = sg->side[0];
-            LCU_CUDA(cudaEventRecord(sg->fork, sg->main));  // the push lane starts where the stream stands now
-            LCU_CUDA(cudaStreamWaitEvent(push_lane[k], sg->fork, 0));
-            sg->side_dirty[0] = true;  // joined into the main stream below
+            LCU_CUDA(cudaEventRecord(sg->side_done[0], sg->side[0]));
+            LCU_CUDA(cudaStreamWaitEvent(sg->main, sg->side_done[0], 0));
+            sg->side_dirty[0] = false;
         }
-    }
-    // pieces outermost, devices innermost: every device gets its first work within microseconds of the call
-    bool more = true;
-    for (size_t piece = 0; more; ++piece) {
-        more = false;
-        for (int k = 0; k < parts; ++k) {
-            const size_t shard = off[k + 1] - off[k];
-            if (kPiece != ~(size_t)0 ? piece * kPiece >= shard : piece > 0 || shard == 0) continue;
-            const size_t p = off[k] + (kPiece != ~(size_t)0 ? piece * kPiece : 0);
-            const size_t n = (kPiece == ~(size_t)0 || off[k + 1] - p < kPiece) ? off[k + 1] - p : kPiece;
-            if (p + n < off[k + 1]) more = true;
-            const int g = owners[k];
-            LibreCUstream sg = streams[g];
-            LIBRECUDA_ERR_PROPAGATE(bind(sg->ctx));
-            uint8_t *mine = static_cast<uint8_t *>(bufs[g]);
-            // The pull shares the root's port with all the other devices, so it is slow by construction; with a
-            // full grid its waiting CTAs would fill every SM and starve the forwarding kernels of this device
-            // (measured: the broadcast took twice as long).  74 looping CTAs carry the pull's share comfortably.
-            if (push_lane[k] == nullptr) LCU_LCB(lcb_copy_d2d(mine + p, src + p, n, sg->main));
-            else LCU_LCB(lcb_copy_d2d_ex(mine + p, src + p, n, LCB_COPY_VEC, pull_ctas, sg->main));
-            if (push_lane[k] == nullptr) continue;
-            cudaEvent_t landed;
-            LCU_CUDA(cudaEventCreateWithFlags(&landed, cudaEventDisableTiming));
-            to_destroy.push_back(landed);
-            LCU_CUDA(cudaEventRecord(landed, sg->main));
-            LCU_CUDA(cudaStreamWaitEvent(push_lane[k], landed, 0));
-            for (int step = 1; step < parts; ++step) {  // rotate the targets so the stores spread over the peers
-                const int q = owners[(k + step) % parts];
-                LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[q]) + p, mine + p, n, push_lane[k]));
-            }
-        }
-    }
-    for (int k = 0; k < parts; ++k) {
-        LibreCUstream sg = streams[owners[k]];
-        if (!sg->side_dirty[0]) continue;
-        LIBRECUDA_ERR_PROPAGATE(bind(sg->ctx));
-        LCU_CUDA(cudaEventRecord(sg->side_done[0], sg->side[0]));
-        LCU_CUDA(cudaStreamWaitEvent(sg->main, sg->side_done[0], 0));
-        sg->side_dirty[0] = false;
-    }
-    for (cudaEvent_t e : to_destroy) (void)cudaEventDestroy(e);
-    LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
-    return rebind_current();
+        for (cudaEvent_t e : to_destroy) (void)cudaEventDestroy(e);
+        LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+        return rebind_current();
+    });
 }
 
 // ---- inter-process sharing -------------------------------------------------------------------------------------

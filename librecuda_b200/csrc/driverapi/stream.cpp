@@ -181,17 +181,19 @@ libreCudaStatus_t commence(LibreCUstream st) {
 // ---- streams ----------------------------------------------------------------------------------------------
 
 libreCudaStatus_t libreCuStreamCreate(LibreCUstream *pStreamOut, uint32_t flags) {
-    (void)flags;
-    LIBRECUDA_VALIDATE(pStreamOut != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    LCU_ENSURE_CTX();
-    LibreCUcontext ctx = globals().current;
-    LIBRECUDA_ERR_PROPAGATE(bind(ctx));
-    auto st = std::make_unique<LibreCUstream_>();
-    st->ctx = ctx;
-    LCU_CUDA(cudaStreamCreateWithFlags(&st->main, cudaStreamNonBlocking));
-    LCU_CUDA(cudaEventCreateWithFlags(&st->fork, cudaEventDisableTiming));
-    *pStreamOut = st.release();
-    LIBRECUDA_SUCCEED();
+    return lcu_guarded([&]() -> libreCudaStatus_t {
+        (void)flags;
+        LIBRECUDA_VALIDATE(pStreamOut != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LCU_ENSURE_CTX();
+        LibreCUcontext ctx = globals().current;
+        LIBRECUDA_ERR_PROPAGATE(bind(ctx));
+        auto st = std::make_unique<LibreCUstream_>();
+        st->ctx = ctx;
+        LCU_CUDA(cudaStreamCreateWithFlags(&st->main, cudaStreamNonBlocking));
+        LCU_CUDA(cudaEventCreateWithFlags(&st->fork, cudaEventDisableTiming));
+        *pStreamOut = st.release();
+        LIBRECUDA_SUCCEED();
+    });
 }
 
 libreCudaStatus_t libreCuStreamDestroy(LibreCUstream stream) {
@@ -217,8 +219,10 @@ libreCudaStatus_t libreCuStreamDestroy(LibreCUstream stream) {
 }
 
 libreCudaStatus_t libreCuStreamCommence(LibreCUstream stream) {
-    LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    return commence(stream);
+    return lcu_guarded([&]() -> libreCudaStatus_t {
+        LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        return commence(stream);
+    });
 }
 
 libreCudaStatus_t libreCuStreamAwait(LibreCUstream stream) {
@@ -266,11 +270,13 @@ static libreCudaStatus_t record_copy(void *dst, const void *src, size_t n, Libre
 }
 
 libreCudaStatus_t libreCuMemCpy(void *dst, void *src, size_t byteCount, LibreCUstream stream, bool async) {
-    LIBRECUDA_VALIDATE(dst != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    LIBRECUDA_VALIDATE(src != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    LCU_ENSURE_CTX();
-    return record_copy(dst, src, byteCount, stream, async, classify(dst), classify(src));
+    return lcu_guarded([&]() -> libreCudaStatus_t {
+        LIBRECUDA_VALIDATE(dst != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(src != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LCU_ENSURE_CTX();
+        return record_copy(dst, src, byteCount, stream, async, classify(dst), classify(src));
+    });
 }
 
 static libreCudaStatus_t directional(void *dst, const void *src, size_t n, LibreCUstream stream, bool async,
@@ -343,22 +349,26 @@ libreCudaStatus_t libreCuMemsetD32Async(void *d, unsigned int v, size_t n, Libre
 // ---- events -----------------------------------------------------------------------------------------------
 
 libreCudaStatus_t libreCuEventCreate(LibreCUEvent *pEventOut, uint32_t flags) {
-    (void)flags;
-    LIBRECUDA_VALIDATE(pEventOut != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    *pEventOut = new LibreCUEvent_();
-    LIBRECUDA_SUCCEED();
+    return lcu_guarded([&]() -> libreCudaStatus_t {
+        (void)flags;
+        LIBRECUDA_VALIDATE(pEventOut != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        *pEventOut = new LibreCUEvent_();
+        LIBRECUDA_SUCCEED();
+    });
 }
 
 libreCudaStatus_t libreCuEventRecord(LibreCUEvent event, LibreCUstream stream) {
-    LIBRECUDA_VALIDATE(event != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    event->stream = stream;
-    event->ctx = stream->ctx;
-    event->state = LibreCUEvent_::Pending;
-    Command c;
-    c.kind = Command::EventRecord;
-    c.event = event;
-    return record(stream, std::move(c));
+    return lcu_guarded([&]() -> libreCudaStatus_t {
+        LIBRECUDA_VALIDATE(event != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        event->stream = stream;
+        event->ctx = stream->ctx;
+        event->state = LibreCUEvent_::Pending;
+        Command c;
+        c.kind = Command::EventRecord;
+        c.event = event;
+        return record(stream, std::move(c));
+    });
 }
 
 libreCudaStatus_t libreCuEventSynchronize(LibreCUEvent event) {
@@ -421,11 +431,13 @@ libreCudaStatus_t libreCuEventDestroy(LibreCUEvent event) {
 }
 
 libreCudaStatus_t libreCuStreamWaitEvent(LibreCUstream stream, LibreCUEvent event) {
-    LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    LIBRECUDA_VALIDATE(event != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-    LIBRECUDA_VALIDATE(event->state != LibreCUEvent_::Never, LIBRECUDA_ERROR_INVALID_VALUE);
-    Command c;
-    c.kind = Command::WaitEvent;
-    c.event = event;
-    return record(stream, std::move(c));
+    return lcu_guarded([&]() -> libreCudaStatus_t {
+        LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(event != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(event->state != LibreCUEvent_::Never, LIBRECUDA_ERROR_INVALID_VALUE);
+        Command c;
+        c.kind = Command::WaitEvent;
+        c.event = event;
+        return record(stream, std::move(c));
+    });
 }
