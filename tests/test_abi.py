@@ -116,3 +116,18 @@ def test_partition_plan_rejects_bad_arguments():
     assert N.lib.libreCuPartitionPlan(100, 0, 16, out) == api.ERROR_INVALID_VALUE
     assert N.lib.libreCuPartitionPlan(100, 2, 24, out) == api.ERROR_INVALID_VALUE
     assert N.lib.libreCuPartitionPlan(100, 2, 16, None) == api.ERROR_INVALID_VALUE
+
+
+def test_tunables_roundtrip_and_environment_override():
+    import subprocess
+    import sys
+
+    assert N.lib.lcb_tune(b"bcast_piece_mib", 48) == 0 and N.lib.lcb_tune_get(b"bcast_piece_mib") == 48
+    assert N.lib.lcb_tune(b"reset", 0) == 0 and N.lib.lcb_tune_get(b"bcast_piece_mib") == 64
+    assert N.lib.lcb_tune_get(b"no_such_knob") == -1
+    code = ("from librecuda_b200 import _native as N; "
+            "print(N.lib.lcb_tune_get(b'a2a_ctas_sm'), N.lib.lcb_tune_get(b'pdl'), N.lib.lcb_tune_get(b'auto_tma_min_mib'))")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=str(INCLUDE.parent),
+                         env={**__import__("os").environ, "LCB_TUNE": "a2a_ctas_sm=7,pdl=0,bogus=3"})
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.split() == ["7", "0", "2048"]
