@@ -471,8 +471,18 @@ def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_r
     measure("p2p_shift_pull_1GiB", lambda: api.lcb_check(lib.lcb_copy_d2d(recv.ptr, prev_send, shard, native), "peer pull"), shard)
     measure("p2p_shift_push_1GiB", lambda: api.lcb_check(lib.lcb_copy_d2d(nxt_recv, send.ptr, shard, native), "peer push"), shard)
 
+    measure("p2p_shift_copy_engine_1GiB", lambda: api.lcb_check(lib.lcb_vendor_memcpy_d2d(nxt_recv, send.ptr, shard, native), "peer engine"), shard)
+
     # 2. all-to-all, own kernels: one launch per rank moves every chunk (pull = remote loads, push = remote stores)
     measure("alltoall_own_push", lambda: api.lcb_check(lib.lcb_alltoall_push(peer_arr, send.ptr, chunk, G, rank, native), "a2a push"), (G - 1) * chunk)
+    def a2a_engine():
+        # the same exchange as G-1 copy-engine peer copies per rank, rotated so every GPU has one sender per step
+        for step in range(1, G):
+            j = (rank + step) % G
+            api.lcb_check(lib.lcb_vendor_memcpy_d2d(peers[j] + rank * chunk, send.ptr + j * chunk, chunk, native), "a2a engine")
+        api.lcb_check(lib.lcb_copy_d2d(recv.ptr + rank * chunk, send.ptr + rank * chunk, chunk, native), "a2a self")
+
+    measure("alltoall_copy_engines", a2a_engine, (G - 1) * chunk)
     stream.memset_d8(recv, 0, G * chunk)
     stream.run()
     measure("alltoall_own_pull", lambda: api.lcb_check(lib.lcb_alltoall_pull(send_arr, recv.ptr, chunk, G, rank, native), "a2a pull"), (G - 1) * chunk)

@@ -211,8 +211,9 @@ LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAllPush(void *const *peerRecvBufs
 // complete before this runs and unchanged until every rank has finished.
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAllPull(void *const *peerSendBufs, void *recvBuf, size_t chunkBytes, int nRanks, int rank, LibreCUstream stream);
 // Single-process collectives over the devices of `streams[0..nDev)` (one stream per device, peer
-// access enabled).  useNccl != 0 runs them through NCCL (ncclSend/ncclRecv, ncclBroadcast);
-// useNccl == 0 runs the library's own peer-memory kernels.
+// access enabled).  useNccl == 1 runs them through NCCL (ncclSend/ncclRecv, ncclBroadcast); useNccl == 0 runs
+// the library's own peer-memory kernels; libreCuAllToAll also takes 2: the exchange as G-1 copy-engine peer
+// copies per GPU (the fastest form measured on NVLink 5 when all GPUs exchange at once).
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, size_t chunkBytes, int nDev, const LibreCUstream *streams, int useNccl);
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount, int nDev, const LibreCUstream *streams, int useNccl);
 

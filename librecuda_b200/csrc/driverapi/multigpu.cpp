@@ -245,13 +245,46 @@ libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, 
         std::vector<int> devs;
         LIBRECUDA_ERR_PROPAGATE(check_group(nDev, streams, &devs));
         for (int r = 0; r < nDev; ++r) LIBRECUDA_VALIDATE(recvBufs[r] != nullptr && sendBufs[r] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-        if (!useNccl) {
+        LIBRECUDA_VALIDATE(useNccl >= 0 && useNccl <= 2, LIBRECUDA_ERROR_INVALID_VALUE);
+        if (useNccl != 1) {
             LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, recvBufs));
             LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, sendBufs));
         }
         for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(commence(streams[r]));
         if (chunkBytes == 0) LIBRECUDA_SUCCEED();
-        if (useNccl) {
+        if (useNccl == 2) {
+            // copy engines: rank r sends chunk (r+s) mod n to rank (r+s) mod n at step s, so that at every step
+            // each GPU receives from exactly one sender; its own chunk goes through the local copy kernel
+            LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+            for (int r = 0; r < nDev; ++r) {
+                // the local chunk runs as a kernel on a side lane, beside the engine copies of the main lane
+                LibreCUstream sr = streams[r];
+                LIBRECUDA_ERR_PROPAGATE(bind(sr->ctx));
+                if (sr->side[0] == nullptr) {
+                    LCU_CUDA(cudaStreamCreateWithFlags(&sr->side[0], cudaStreamNonBlocking));
+                    LCU_CUDA(cudaEventCreateWithFlags(&sr->side_done[0], cudaEventDisableTiming));
+                }
+                LCU_CUDA(cudaEventRecord(sr->fork, sr->main));
+                LCU_CUDA(cudaStreamWaitEvent(sr->side[0], sr->fork, 0));
+                LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(recvBufs[r]) + (size_t)r * chunkBytes,
+                                     static_cast<const uint8_t *>(sendBufs[r]) + (size_t)r * chunkBytes, chunkBytes, sr->side[0]));
+                LCU_CUDA(cudaEventRecord(sr->side_done[0], sr->side[0]));
+            }
+            for (int step = 1; step < nDev; ++step) {
+                for (int r = 0; r < nDev; ++r) {
+                    const int j = (r + step) % nDev;
+                    LIBRECUDA_ERR_PROPAGATE(bind(streams[r]->ctx));
+                    uint8_t *d = static_cast<uint8_t *>(recvBufs[j]) + (size_t)r * chunkBytes;
+                    const uint8_t *s = static_cast<const uint8_t *>(sendBufs[r]) + (size_t)j * chunkBytes;
+                    LCU_CUDA(cudaMemcpyAsync(d, s, chunkBytes, cudaMemcpyDefault, streams[r]->main));
+                }
+            }
+            for (int r = 0; r < nDev; ++r) {
+                LIBRECUDA_ERR_PROPAGATE(bind(streams[r]->ctx));
+                LCU_CUDA(cudaStreamWaitEvent(streams[r]->main, streams[r]->side_done[0], 0));
+            }
+            LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+        } else if (useNccl == 1) {
             Nccl *n = nccl();
             LIBRECUDA_VALIDATE(n != nullptr, LIBRECUDA_ERROR_NOT_FOUND);
             LIBRECUDA_ERR_PROPAGATE(nccl_group_for(n, devs));
@@ -289,6 +322,7 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
         LIBRECUDA_ERR_PROPAGATE(check_group(nDev, streams, &devs));
         LIBRECUDA_VALIDATE(root >= 0 && root < nDev, LIBRECUDA_ERROR_INVALID_VALUE);
         for (int r = 0; r < nDev; ++r) LIBRECUDA_VALIDATE(bufs[r] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(useNccl == 0 || useNccl == 1, LIBRECUDA_ERROR_INVALID_VALUE);
         if (!useNccl) LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, bufs));
         for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(commence(streams[r]));
         if (byteCount == 0 || nDev == 1) LIBRECUDA_SUCCEED();

@@ -42,6 +42,7 @@ struct Tuning {
     int tma2_depth;          // two-issuer ring: store groups that may still be reading shared memory
     int tma2_stages;         // two-issuer ring: stages
     int tma2_chunk;          // two-issuer ring: bytes per bulk copy
+    int peer_copy_engine;    // 1: libreCuMemCpy / libreCuMemcpyPeer between two GPUs (>= 1 MiB) use the copy engines
     int bcast_piece_mib;     // own broadcast: MiB per pipelined piece
     int bcast_pull_ctas;     // own broadcast: CTAs of the kernel that pulls from the root (it must not fill the GPU)
 };

@@ -40,6 +40,7 @@ static const Tuning kDefaults = {
         /*tma2_depth*/ 2,
         /*tma2_stages*/ 8,
         /*tma2_chunk*/ 8192,
+        /*peer_copy_engine*/ 1,
         /*bcast_piece_mib*/ 64,
         /*bcast_pull_ctas*/ 74,
 };
@@ -121,6 +122,7 @@ extern "C" int lcb_tune(const char *name, int value) {
     LCB_KNOB(tma2_depth)
     LCB_KNOB(tma2_stages)
     LCB_KNOB(tma2_chunk)
+    LCB_KNOB(peer_copy_engine)
     LCB_KNOB(bcast_piece_mib)
     LCB_KNOB(bcast_pull_ctas)
 #undef LCB_KNOB
@@ -134,6 +136,7 @@ extern "C" int lcb_tune_get(const char *name) {
     if (std::strcmp(name, #field) == 0) return tuning().field;
     LCB_KNOB(bcast_piece_mib)
     LCB_KNOB(bcast_pull_ctas)
+    LCB_KNOB(peer_copy_engine)
     LCB_KNOB(a2a_ctas_sm)
     LCB_KNOB(pdl)
     LCB_KNOB(auto_tma_min_mib)

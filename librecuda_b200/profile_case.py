@@ -111,6 +111,15 @@ def multigpu(n_gpus: int, nbytes: int, reps: int):
         print(f"broadcast  {name:12s} {t * 1e3:8.3f} ms  {nbytes / t / 1e9:7.1f} GB/s")
         t = timed(lambda: lib.libreCuAllToAll(rp, sp, chunk, G, stp, use_nccl))
         print(f"all-to-all {name:12s} {t * 1e3:8.3f} ms  {(G - 1) * chunk / t / 1e9:7.1f} GB/s per GPU")
+    t = timed(lambda: lib.libreCuAllToAll(rp, sp, chunk, G, stp, 2))
+    print(f"all-to-all {'copy engines':12s} {t * 1e3:8.3f} ms  {(G - 1) * chunk / t / 1e9:7.1f} GB/s per GPU")
+    # one peer copy through libreCuMemCpy, device 0 -> device 1: copy engine (default) against the copy kernel
+    for engine in (1, 0):
+        api.tune(peer_copy_engine=engine)
+        t = timed(lambda: lib.libreCuMemCpy(bufs[1].ptr, bufs[0].ptr, nbytes, streams[0].handle, False)
+                  or lib.libreCuStreamCommence(streams[0].handle))
+        print(f"peer copy  {'engine' if engine else 'kernel':12s} {t * 1e3:8.3f} ms  {nbytes / t / 1e9:7.1f} GB/s")
+    api.tune_reset()
 
 
 def main():

@@ -59,8 +59,18 @@ def _download(ctxs, streams, g, buf, nbytes):
     return out
 
 
+@pytest.mark.parametrize("engine", [0, 1])
 @pytest.mark.parametrize("so,do", [(0, 0), (1, 0), (16, 3)])
-def test_peer_copy_push_and_pull(gpus, so, do):
+def test_peer_copy_push_and_pull(gpus, so, do, engine):
+    # engine = 1: large cross-GPU copies go to the copy engines (the default); 0: this library's copy kernel
+    api.tune(peer_copy_engine=engine)
+    try:
+        _peer_copy_push_and_pull(gpus, so, do)
+    finally:
+        api.tune_reset()
+
+
+def _peer_copy_push_and_pull(gpus, so, do):
     ctxs, streams = gpus
     n = 9 * MiB + 77
     src_h = oracle.random_bytes(n + 64, seed=3)
@@ -119,7 +129,7 @@ def test_partitioned_copy_scatter(gpus):
     src.free()
 
 
-@pytest.mark.parametrize("use_nccl", [0, 1])
+@pytest.mark.parametrize("use_nccl", [0, 1, 2])
 def test_all_to_all(gpus, use_nccl):
     ctxs, streams = gpus
     G = len(ctxs)
