@@ -201,6 +201,10 @@ def test_device_helpers_agree_with_oracle(stream):
     for m in (n, n - 5, 8, 3, 4096):
         assert device_checksum(stream, buf.ptr, m, scratch, out) == oracle.checksum64(want[:m])
         assert device_checksum(stream, buf.ptr, m, scratch, out) == oracle.checksum64(want[:m])  # scratch is reusable
+    # the kernel reads 16-byte pairs: a source 8 but not 16 bytes aligned, odd and even word counts, no pair at all
+    for off in (8, 24):
+        for m in (0, 1, 8, 15, 16, 17, 24, 4096 + 8, 3 * MiB - 24, 3 * MiB - 19):
+            assert device_checksum(stream, buf.ptr + off, m, scratch, out) == oracle.checksum64(want[off:off + m]), (off, m)
     other = api.DeviceBuffer(n + 8)
     to_device(stream, other, want)
     assert device_compare(stream, buf.ptr, other.ptr, n, res) == (0, 2**64 - 1)
