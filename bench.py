@@ -468,38 +468,76 @@ def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_r
     #    pull = the destination GPU loads from the source GPU (faster direction), push = the source GPU stores.
     prev_send = send_peers[(rank - 1) % G]
     nxt_recv = peers[(rank + 1) % G]
-    measure("p2p_shift_pull_1GiB", lambda: api.lcb_check(lib.lcb_copy_d2d(recv.ptr, prev_send, shard, native), "peer pull"), shard)
-    measure("p2p_shift_push_1GiB", lambda: api.lcb_check(lib.lcb_copy_d2d(nxt_recv, send.ptr, shard, native), "peer push"), shard)
+    shifts = (
+        ("p2p_shift_pull_1GiB", lambda: api.lcb_check(lib.lcb_copy_d2d(recv.ptr, prev_send, shard, native), "peer pull")),
+        ("p2p_shift_push_1GiB", lambda: api.lcb_check(lib.lcb_copy_d2d(nxt_recv, send.ptr, shard, native), "peer push")),
+        ("p2p_shift_copy_engine_1GiB", lambda: api.lcb_check(lib.lcb_vendor_memcpy_d2d(nxt_recv, send.ptr, shard, native), "peer engine")),
+    )
+    res_shift = api.DeviceBuffer(16)
+    expect = api.DeviceBuffer(shard)
+    api.lcb_check(lib.lcb_fill_splitmix64(expect.ptr, shard, 100 + (rank - 1) % G, native), "fill")  # the previous rank's send buffer
+    for name, fn in shifts:
+        barrier()
+        stream.memset_d8(recv, 0, shard)
+        stream.run()
+        barrier()
+        measure(name, fn, shard)
+        api.lcb_check(lib.lcb_compare_bytes(recv.ptr, expect.ptr, shard, res_shift.ptr, native), "cmp")
+        got = np.zeros(2, np.uint64)
+        stream.memcpy(got, res_shift, 16)
+        stream.run()
+        out[name]["verified"] = int(got[0]) == 0
+    expect.free()
+    res_shift.free()
 
-    measure("p2p_shift_copy_engine_1GiB", lambda: api.lcb_check(lib.lcb_vendor_memcpy_d2d(nxt_recv, send.ptr, shard, native), "peer engine"), shard)
+    # 2. all-to-all: one fused kernel per rank (push = remote stores, pull = remote loads) and the copy-engine form.
+    #    Each form starts from a zeroed receive buffer and is verified on the device afterwards.
+    resb = api.DeviceBuffer(16)
 
-    # 2. all-to-all, own kernels: one launch per rank moves every chunk (pull = remote loads, push = remote stores)
-    measure("alltoall_own_push", lambda: api.lcb_check(lib.lcb_alltoall_push(peer_arr, send.ptr, chunk, G, rank, native), "a2a push"), (G - 1) * chunk)
+    def clear_recv():
+        barrier()
+        stream.memset_d8(recv, 0, G * chunk)
+        stream.run()
+        barrier()
+
+    def verify_recv():
+        # slot r of my receive buffer must be chunk `rank` of rank r's send buffer
+        barrier()
+        ok = True
+        for r in range(G):
+            # regenerate rank r's send buffer up to chunk `rank` (the generator is keyed by position)
+            full = api.DeviceBuffer((rank + 1) * chunk)
+            api.lcb_check(lib.lcb_fill_splitmix64(full.ptr, (rank + 1) * chunk, 100 + r, native), "fill")
+            api.lcb_check(lib.lcb_compare_bytes(recv.ptr + r * chunk, full.ptr + rank * chunk, chunk, resb.ptr, native), "cmp")
+            got = np.zeros(2, np.uint64)
+            stream.memcpy(got, resb, 16)
+            stream.run()
+            ok = ok and int(got[0]) == 0
+            full.free()
+        return ok
+
+    side = api.Stream()
+
     def a2a_engine():
-        # the same exchange as G-1 copy-engine peer copies per rank, rotated so every GPU has one sender per step
+        # G-1 copy-engine peer copies per rank, rotated so every GPU has one sender per step; the local chunk
+        # runs as a kernel on a second stream beside them (forked from and joined to the timed one)
+        api.lcb_check(lib.lcb_stream_wait_stream(side.native, native), "fork")
+        api.lcb_check(lib.lcb_copy_d2d(recv.ptr + rank * chunk, send.ptr + rank * chunk, chunk, side.native), "a2a self")
         for step in range(1, G):
             j = (rank + step) % G
             api.lcb_check(lib.lcb_vendor_memcpy_d2d(peers[j] + rank * chunk, send.ptr + j * chunk, chunk, native), "a2a engine")
-        api.lcb_check(lib.lcb_copy_d2d(recv.ptr + rank * chunk, send.ptr + rank * chunk, chunk, native), "a2a self")
+        api.lcb_check(lib.lcb_stream_wait_stream(native, side.native), "join")
 
-    measure("alltoall_copy_engines", a2a_engine, (G - 1) * chunk)
-    stream.memset_d8(recv, 0, G * chunk)
-    stream.run()
-    measure("alltoall_own_pull", lambda: api.lcb_check(lib.lcb_alltoall_pull(send_arr, recv.ptr, chunk, G, rank, native), "a2a pull"), (G - 1) * chunk)
-    # verify: slot r of my recv buffer must be chunk `rank` of rank r's send buffer
-    ok = True
-    resb = api.DeviceBuffer(16)
-    for r in range(G):
-        # regenerate rank r's send buffer up to chunk `rank` (the generator is keyed by position)
-        full = api.DeviceBuffer((rank + 1) * chunk)
-        api.lcb_check(lib.lcb_fill_splitmix64(full.ptr, (rank + 1) * chunk, 100 + r, native), "fill")
-        api.lcb_check(lib.lcb_compare_bytes(recv.ptr + r * chunk, full.ptr + rank * chunk, chunk, resb.ptr, native), "cmp")
-        got = np.zeros(2, np.uint64)
-        stream.memcpy(got, resb, 16)
-        stream.run()
-        ok = ok and int(got[0]) == 0
-        full.free()
-    out["alltoall_own_pull"]["verified"] = ok
+    forms = (
+        ("alltoall_own_push", lambda: api.lcb_check(lib.lcb_alltoall_push(peer_arr, send.ptr, chunk, G, rank, native), "a2a push")),
+        ("alltoall_copy_engines", a2a_engine),
+        ("alltoall_own_pull", lambda: api.lcb_check(lib.lcb_alltoall_pull(send_arr, recv.ptr, chunk, G, rank, native), "a2a pull")),
+    )
+    for name, fn in forms:
+        clear_recv()
+        measure(name, fn, (G - 1) * chunk)
+        out[name]["verified"] = verify_recv()
+    side.destroy()
 
     # 3. partitioned copy of an 8 GiB buffer that lives on rank 0: shard g (2 MiB-aligned boundaries from
     #    libreCuPartitionPlan) is pulled by rank g into its own memory; rank 0 keeps shard 0 with a local copy.

@@ -139,6 +139,9 @@ int lcb_timer_stop(void *timer, lcbStream stream);
 int lcb_timer_elapsed_ms(void *timer, float *ms_out);
 int lcb_timer_destroy(void *timer);
 int lcb_stream_synchronize(lcbStream stream);
+/* Work submitted to `waiter` after this call starts only when everything submitted to `signaller` before it
+ * has finished (an event recorded on one stream and awaited by the other; the host does not block). */
+int lcb_stream_wait_stream(lcbStream waiter, lcbStream signaller);
 
 /* The CUDA runtime's own device-to-device copy and memset on the same stream, exported only so that the
  * benchmark can time them beside this library's kernels.  Nothing in the library calls them. */

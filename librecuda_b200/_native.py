@@ -52,6 +52,7 @@ LCB_FUNCTIONS = {
     "lcb_timer_elapsed_ms": (i32, [vp, C.POINTER(C.c_float)]),
     "lcb_timer_destroy": (i32, [vp]),
     "lcb_stream_synchronize": (i32, [vp]),
+    "lcb_stream_wait_stream": (i32, [vp, vp]),
     "lcb_vendor_memcpy_d2d": (i32, [vp, vp, sz, vp]),
     "lcb_vendor_memset_d8": (i32, [vp, C.c_ubyte, sz, vp]),
 }

@@ -201,6 +201,16 @@ extern "C" int lcb_stream_synchronize(lcbStream stream) {
     return (int)cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int lcb_stream_wait_stream(lcbStream waiter, lcbStream signaller) {
+    cudaEvent_t ev = nullptr;
+    cudaError_t err = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (err != cudaSuccess) return (int)err;
+    err = cudaEventRecord(ev, static_cast<cudaStream_t>(signaller));
+    if (err == cudaSuccess) err = cudaStreamWaitEvent(static_cast<cudaStream_t>(waiter), ev, 0);
+    (void)cudaEventDestroy(ev);  // released by the runtime once the wait has consumed it
+    return (int)err;
+}
+
 // ---- vendor paths, for side-by-side measurement only (never used by the library's own data path) ---------
 extern "C" int lcb_vendor_memcpy_d2d(void *dst, const void *src, size_t bytes, lcbStream stream) {
     return (int)cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream));
