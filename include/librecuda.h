@@ -212,8 +212,9 @@ LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAllPush(void *const *peerRecvBufs
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAllPull(void *const *peerSendBufs, void *recvBuf, size_t chunkBytes, int nRanks, int rank, LibreCUstream stream);
 // Single-process collectives over the devices of `streams[0..nDev)` (one stream per device, peer
 // access enabled).  useNccl == 1 runs them through NCCL (ncclSend/ncclRecv, ncclBroadcast); useNccl == 0 runs
-// the library's own peer-memory kernels; libreCuAllToAll also takes 2: the exchange as G-1 copy-engine peer
-// copies per GPU (the fastest form measured on NVLink 5 when all GPUs exchange at once).
+// the library's own peer-memory kernels; useNccl == 2 runs them on the copy engines: the all-to-all as G-1
+// rotated peer copies per GPU (the fastest form measured on NVLink 5 when all GPUs exchange at once), the
+// broadcast as a chain root -> next device -> ... pipelined in pieces with one event per piece and hop.
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, size_t chunkBytes, int nDev, const LibreCUstream *streams, int useNccl);
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount, int nDev, const LibreCUstream *streams, int useNccl);
 

@@ -10,6 +10,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <cmath>
 #include <cstring>
 
 #include "internal.h"
@@ -322,11 +323,54 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
         LIBRECUDA_ERR_PROPAGATE(check_group(nDev, streams, &devs));
         LIBRECUDA_VALIDATE(root >= 0 && root < nDev, LIBRECUDA_ERROR_INVALID_VALUE);
         for (int r = 0; r < nDev; ++r) LIBRECUDA_VALIDATE(bufs[r] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-        LIBRECUDA_VALIDATE(useNccl == 0 || useNccl == 1, LIBRECUDA_ERROR_INVALID_VALUE);
-        if (!useNccl) LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, bufs));
+        LIBRECUDA_VALIDATE(useNccl >= 0 && useNccl <= 2, LIBRECUDA_ERROR_INVALID_VALUE);
+        if (useNccl != 1) LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, bufs));
         for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(commence(streams[r]));
         if (byteCount == 0 || nDev == 1) LIBRECUDA_SUCCEED();
-        if (useNccl) {
+        if (useNccl == 2) {
+            // Copy-engine chain: root -> d1 -> d2 -> ... in device order, piece by piece.  The stream of chain
+            // member h pushes piece p to member h+1 as soon as member h-1 has delivered it (one event per piece
+            // and hop), so every GPU receives and sends at the engines' rate at once.  Time = bytes / rate
+            // + pieces * c + (members - 2) * piece / rate, where c, the cost of one dependent peer copy, measured
+            // 7-12 us (4 GPUs, 4 GiB: 571 / 623 / 671 / 686 GB/s with 16 / 32 / 64 / 128 MiB pieces; alternating
+            // the pieces over two lanes per member changed nothing, so the cost sits in the engine, not in the
+            // lane).  The piece that minimises it is sqrt(bytes * c * rate / (members - 2)), c * rate = 7.75 MB.
+            std::vector<int> chain;
+            for (int k = 0; k < nDev; ++k) chain.push_back((root + k) % nDev);
+            size_t piece = byteCount;
+            if (nDev > 2) {
+                const int piece_mib = lcb_tune_get("bcast_engine_piece_mib");
+                if (piece_mib > 0) {
+                    piece = (size_t)piece_mib << 20;
+                } else {
+                    const double best = std::sqrt((double)byteCount * 7.75e6 / (double)(nDev - 2));
+                    piece = ((size_t)(best / 1048576.0) + 1) << 20;
+                }
+            }
+            LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+            std::vector<cudaEvent_t> arrived(nDev, nullptr);  // arrived[h]: the current piece has reached member h
+            for (size_t p = 0; p < byteCount; p += piece) {
+                const size_t n = byteCount - p < piece ? byteCount - p : piece;
+                for (int h = 0; h + 1 < nDev; ++h) {
+                    LibreCUstream sh = streams[chain[h]];
+                    LIBRECUDA_ERR_PROPAGATE(bind(sh->ctx));
+                    if (h > 0) {
+                        LCU_CUDA(cudaStreamWaitEvent(sh->main, arrived[h], 0));
+                        (void)cudaEventDestroy(arrived[h]);  // released once the wait has consumed it
+                        arrived[h] = nullptr;
+                    }
+                    LCU_CUDA(cudaMemcpyAsync(static_cast<uint8_t *>(bufs[chain[h + 1]]) + p,
+                                             static_cast<const uint8_t *>(bufs[chain[h]]) + p, n, cudaMemcpyDefault, sh->main));
+                    if (h + 2 < nDev) {
+                        LCU_CUDA(cudaEventCreateWithFlags(&arrived[h + 1], cudaEventDisableTiming));
+                        LCU_CUDA(cudaEventRecord(arrived[h + 1], sh->main));
+                    }
+                }
+            }
+            LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+            return rebind_current();
+        }
+        if (useNccl == 1) {
             Nccl *n = nccl();
             LIBRECUDA_VALIDATE(n != nullptr, LIBRECUDA_ERROR_NOT_FOUND);
             LIBRECUDA_ERR_PROPAGATE(nccl_group_for(n, devs));

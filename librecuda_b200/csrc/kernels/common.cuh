@@ -45,6 +45,7 @@ struct Tuning {
     int peer_copy_engine;    // 1: libreCuMemCpy / libreCuMemcpyPeer between two GPUs (>= 1 MiB) use the copy engines
     int bcast_piece_mib;     // own broadcast: MiB per pipelined piece
     int bcast_pull_ctas;     // own broadcast: CTAs of the kernel that pulls from the root (it must not fill the GPU)
+    int bcast_engine_piece_mib;  // copy-engine chain broadcast: MiB per piece, 0 = chosen from the size and the number of GPUs
 };
 Tuning &tuning();
 

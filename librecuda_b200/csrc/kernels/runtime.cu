@@ -43,6 +43,7 @@ static const Tuning kDefaults = {
         /*peer_copy_engine*/ 1,
         /*bcast_piece_mib*/ 64,
         /*bcast_pull_ctas*/ 74,
+        /*bcast_engine_piece_mib*/ 0,
 };
 
 Tuning &tuning() {
@@ -125,6 +126,7 @@ extern "C" int lcb_tune(const char *name, int value) {
     LCB_KNOB(peer_copy_engine)
     LCB_KNOB(bcast_piece_mib)
     LCB_KNOB(bcast_pull_ctas)
+    LCB_KNOB(bcast_engine_piece_mib)
 #undef LCB_KNOB
     return 1;
 }
@@ -136,6 +138,7 @@ extern "C" int lcb_tune_get(const char *name) {
     if (std::strcmp(name, #field) == 0) return tuning().field;
     LCB_KNOB(bcast_piece_mib)
     LCB_KNOB(bcast_pull_ctas)
+    LCB_KNOB(bcast_engine_piece_mib)
     LCB_KNOB(peer_copy_engine)
     LCB_KNOB(a2a_ctas_sm)
     LCB_KNOB(pdl)

@@ -111,6 +111,11 @@ def multigpu(n_gpus: int, nbytes: int, reps: int):
         print(f"broadcast  {name:12s} {t * 1e3:8.3f} ms  {nbytes / t / 1e9:7.1f} GB/s")
         t = timed(lambda: lib.libreCuAllToAll(rp, sp, chunk, G, stp, use_nccl))
         print(f"all-to-all {name:12s} {t * 1e3:8.3f} ms  {(G - 1) * chunk / t / 1e9:7.1f} GB/s per GPU")
+    for piece in (0, 32, 64, 128):
+        api.tune(bcast_engine_piece_mib=piece)
+        t = timed(lambda: lib.libreCuBroadcast(bp, 0, nbytes, G, stp, 2))
+        print(f"broadcast  engine chain, {piece or 'auto'} MiB pieces {t * 1e3:8.3f} ms  {nbytes / t / 1e9:7.1f} GB/s")
+    api.tune_reset()
     t = timed(lambda: lib.libreCuAllToAll(rp, sp, chunk, G, stp, 2))
     print(f"all-to-all {'copy engines':12s} {t * 1e3:8.3f} ms  {(G - 1) * chunk / t / 1e9:7.1f} GB/s per GPU")
     # one peer copy through libreCuMemCpy, device 0 -> device 1: copy engine (default) against the copy kernel

@@ -196,12 +196,20 @@ def test_all_to_all_recorded_per_rank(gpus, pull):
     ctxs[0].set_current()
 
 
-@pytest.mark.parametrize("use_nccl", [0, 1])
+@pytest.mark.parametrize("use_nccl", [0, 1, 2])
 @pytest.mark.parametrize("root", [0, 1])
 def test_broadcast(gpus, use_nccl, root):
     ctxs, streams = gpus
     G = len(ctxs)
     n = 37 * MiB + 1001
+    api.tune(bcast_engine_piece_mib=4)     # form 2 with more than two GPUs: ten pieces, the last one ragged
+    try:
+        _broadcast(ctxs, streams, G, n, use_nccl, root)
+    finally:
+        api.tune_reset()
+
+
+def _broadcast(ctxs, streams, G, n, use_nccl, root):
     data = oracle.random_bytes(n, seed=3)
     bufs = [_alloc_on(ctxs[g], n) for g in range(G)]
     for g in range(G):
