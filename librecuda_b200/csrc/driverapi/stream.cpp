@@ -260,11 +260,14 @@ static libreCudaStatus_t record_copy(void *dst, const void *src, size_t n, Libre
             LIBRECUDA_VALIDATE(owner < 0 || stream->ctx->peers.count(owner) != 0, LIBRECUDA_ERROR_INVALID_VALUE);
         }
         c.kind = Command::CopyKernel;  // reference: memcpyD2D, memcopy.cpp:77
-        // Between two different GPUs the copy engines move 775 GB/s per direction with every link busy both
-        // ways, SM-issued stores 707 and loads 645 (NVLink write packets from the SMs carry half the payload
-        // of the engines'); so a large cross-device copy goes to the engines unless the knob says otherwise.
+        // Between two different GPUs the copy engines move 775-782 GB/s per direction, also with every link busy
+        // both ways, where SM-issued stores reach 707-716 and loads 645 (NVLink write packets from the SMs carry
+        // half the payload of the engines'); but every engine peer copy costs 7.7 us on top of its transfer
+        // (measured: 4 GiB cut into 16 ... 2048 back-to-back copies), a kernel launch about 2.5.  The engines
+        // win from about 44 MB up: a cross-device copy of 64 MiB and more goes to them (knob, in MiB; 0 = never).
         const int od = owner_device(dst), os = owner_device(src);
-        if (od >= 0 && os >= 0 && od != os && n >= ((size_t)1 << 20) && lcb_tune_get("peer_copy_engine") == 1) {
+        const int engine_mib = lcb_tune_get("peer_copy_engine");
+        if (od >= 0 && os >= 0 && od != os && engine_mib > 0 && n >= ((size_t)engine_mib << 20)) {
             c.kind = Command::CopyEngine;
             c.copy_kind = cudaMemcpyDefault;
         }

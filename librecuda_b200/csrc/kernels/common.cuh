@@ -42,7 +42,7 @@ struct Tuning {
     int tma2_depth;          // two-issuer ring: store groups that may still be reading shared memory
     int tma2_stages;         // two-issuer ring: stages
     int tma2_chunk;          // two-issuer ring: bytes per bulk copy
-    int peer_copy_engine;    // 1: libreCuMemCpy / libreCuMemcpyPeer between two GPUs (>= 1 MiB) use the copy engines
+    int peer_copy_engine;    // libreCuMemCpy / libreCuMemcpyPeer between two GPUs use the copy engines from this many MiB up; 0 = never
     int bcast_piece_mib;     // own broadcast: MiB per pipelined piece
     int bcast_pull_ctas;     // own broadcast: CTAs of the kernel that pulls from the root (it must not fill the GPU)
     int bcast_engine_piece_mib;  // copy-engine chain broadcast: MiB per piece, 0 = chosen from the size and the number of GPUs

@@ -40,7 +40,7 @@ static const Tuning kDefaults = {
         /*tma2_depth*/ 2,
         /*tma2_stages*/ 8,
         /*tma2_chunk*/ 8192,
-        /*peer_copy_engine*/ 1,
+        /*peer_copy_engine*/ 64,
         /*bcast_piece_mib*/ 64,
         /*bcast_pull_ctas*/ 74,
         /*bcast_engine_piece_mib*/ 0,

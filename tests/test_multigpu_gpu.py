@@ -62,7 +62,7 @@ def _download(ctxs, streams, g, buf, nbytes):
 @pytest.mark.parametrize("engine", [0, 1])
 @pytest.mark.parametrize("so,do", [(0, 0), (1, 0), (16, 3)])
 def test_peer_copy_push_and_pull(gpus, so, do, engine):
-    # engine = 1: large cross-GPU copies go to the copy engines (the default); 0: this library's copy kernel
+    # engine = 1: cross-GPU copies of 1 MiB and more go to the copy engines (by default: from 64 MiB); 0: always the copy kernel
     api.tune(peer_copy_engine=engine)
     try:
         _peer_copy_push_and_pull(gpus, so, do)
