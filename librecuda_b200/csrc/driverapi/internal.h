@@ -202,6 +202,8 @@ namespace lcu {
 libreCudaStatus_t bind(LibreCUcontext ctx);
 libreCudaStatus_t record(LibreCUstream stream, Command &&cmd);
 libreCudaStatus_t commence(LibreCUstream stream);
+// Makes the main lane wait for every side lane that carries async work (the caller has bound the stream's device).
+libreCudaStatus_t join_sides(LibreCUstream stream);
 libreCudaStatus_t host_wait_stream(LibreCUcontext ctx, cudaStream_t s);
 libreCudaStatus_t host_wait_event(LibreCUcontext ctx, cudaEvent_t e);
 bool is_pageable_host(const void *p);

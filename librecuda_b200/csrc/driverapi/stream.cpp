@@ -53,7 +53,7 @@ libreCudaStatus_t host_wait_event(LibreCUcontext ctx, cudaEvent_t e) {
     return host_wait(ctx, [&] { return cudaEventQuery(e); }, [&] { return cudaEventSynchronize(e); });
 }
 
-static libreCudaStatus_t join_sides(LibreCUstream st) {
+libreCudaStatus_t join_sides(LibreCUstream st) {
     for (int i = 0; i < kSideLanes; ++i) {
         if (!st->side_dirty[i]) continue;
         LCU_CUDA(cudaEventRecord(st->side_done[i], st->side[i]));

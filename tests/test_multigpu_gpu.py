@@ -157,6 +157,39 @@ def test_all_to_all(gpus, use_nccl):
     ctxs[0].set_current()
 
 
+@pytest.mark.parametrize("use_nccl", [0, 1, 2])
+def test_collective_starts_after_async_work_recorded_before_it(gpus, use_nccl):
+    # the send buffers are filled by async=true uploads (side lanes of each stream) that are only recorded when
+    # the collective is called: it has to submit them and start after them on every GPU
+    ctxs, streams = gpus
+    G = len(ctxs)
+    chunk = 24 * MiB
+    send_h = [oracle.random_bytes(G * chunk, seed=70 + r) for r in range(G)]
+    want = oracle.alltoall(send_h)
+    send = [_alloc_on(ctxs[g], G * chunk) for g in range(G)]
+    recv = [_alloc_on(ctxs[g], G * chunk) for g in range(G)]
+    for g in range(G):
+        ctxs[g].set_current()
+        streams[g].memset_d8(send[g], 0, G * chunk)
+        streams[g].run()
+        for j in range(G):  # one async upload per chunk: several side lanes in flight
+            streams[g].memcpy(send[g].ptr + j * chunk, send_h[g][j * chunk:(j + 1) * chunk], chunk, async_=True)
+    ctxs[0].set_current()
+    rp = (C.c_void_p * G)(*[b.ptr for b in recv])
+    sp = (C.c_void_p * G)(*[b.ptr for b in send])
+    stp = (C.c_void_p * G)(*[s.handle for s in streams])
+    api.check(lib.libreCuAllToAll(rp, sp, chunk, G, stp, use_nccl))
+    for s in streams:
+        s.await_()
+    for g in range(G):
+        assert np.array_equal(_download(ctxs, streams, g, recv[g], G * chunk), want[g]), f"rank {g}"
+    for g in range(G):
+        ctxs[g].set_current()
+        send[g].free()
+        recv[g].free()
+    ctxs[0].set_current()
+
+
 @pytest.mark.parametrize("pull", [False, True])
 def test_all_to_all_recorded_per_rank(gpus, pull):
     # the per-rank half (push: remote stores, pull: remote loads) is an ordinary recorded stream operation
