@@ -31,21 +31,30 @@ __global__ void __launch_bounds__(512) compare_kernel(const uint64_t *__restrict
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     unsigned long long bad = 0, first = ~0ull;
-    for (size_t i = tid; i < nwords; i += stride) {
-        const uint64_t x = load_shifted(a_al, i, sa8) ^ load_shifted(b_al, i, sb8);
-        if (x) {
-            // count differing bytes, remember the first one
-            int nb = 0, fb = -1;
+    constexpr int kInFlight = 4;  // independent word pairs per thread and iteration (one pair left the kernel latency-bound)
+    for (size_t i = tid; i < nwords; i += stride * kInFlight) {
+        uint64_t x[kInFlight];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                if ((x >> (8 * k)) & 0xff) {
-                    ++nb;
-                    if (fb < 0) fb = k;
+        for (int u = 0; u < kInFlight; ++u) {
+            const size_t p = i + (size_t)u * stride;
+            x[u] = p < nwords ? (load_shifted(a_al, p, sa8) ^ load_shifted(b_al, p, sb8)) : 0ull;
+        }
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+            if (x[u]) {
+                // count differing bytes, remember the first one
+                int nb = 0, fb = -1;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if ((x[u] >> (8 * k)) & 0xff) {
+                        ++nb;
+                        if (fb < 0) fb = k;
+                    }
                 }
+                bad += nb;
+                const unsigned long long pos = (unsigned long long)(i + (size_t)u * stride) * 8 + fb;
+                if (pos < first) first = pos;
             }
-            bad += nb;
-            const unsigned long long pos = (unsigned long long)i * 8 + fb;
-            if (pos < first) first = pos;
         }
     }
     if (tid == 0) {  // trailing bytes, one by one

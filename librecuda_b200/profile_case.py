@@ -129,7 +129,7 @@ def multigpu(n_gpus: int, nbytes: int, reps: int):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["copy", "memset", "index_fill", "axpb", "checksum", "alltoall_self", "sweep", "multigpu"])
+    ap.add_argument("kernel", choices=["copy", "memset", "index_fill", "axpb", "checksum", "compare", "alltoall_self", "sweep", "multigpu"])
     ap.add_argument("--gpus", type=int, default=8)
     ap.add_argument("--max-log2", type=int, default=33)
     ap.add_argument("--bytes", type=int, default=256 << 20)
@@ -152,6 +152,7 @@ def main():
     st.memset_d8(b, 0, n + 4096)
     st.run()
     scratch, out = api.DeviceBuffer(lib.lcb_checksum_scratch_bytes()), api.DeviceBuffer(8)
+    res = api.DeviceBuffer(16)
     peers = (C.c_void_p * 2)(b.ptr, b.ptr + (n // 32) * 16)
 
     def launch():
@@ -165,6 +166,8 @@ def main():
             return lib.lcb_axpb_f32(b.ptr, a.ptr, 2.0, 1.0, n // 4, nat)
         if args.kernel == "checksum":
             return lib.lcb_checksum64(a.ptr, n, scratch.ptr, out.ptr, nat)
+        if args.kernel == "compare":
+            return lib.lcb_compare_bytes(a.ptr + args.src_off, b.ptr + args.dst_off, n, res.ptr, nat)
         # two "ranks" folded onto one GPU: both halves of the send buffer land in this GPU's memory
         return lib.lcb_alltoall_push(peers, a.ptr, (n // 64) * 16, 2, 0, nat)
 
