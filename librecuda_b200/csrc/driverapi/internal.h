@@ -204,6 +204,9 @@ libreCudaStatus_t record(LibreCUstream stream, Command &&cmd);
 libreCudaStatus_t commence(LibreCUstream stream);
 // Makes the main lane wait for every side lane that carries async work (the caller has bound the stream's device).
 libreCudaStatus_t join_sides(LibreCUstream stream);
+// Starts side lane `i` at the main lane's current tail (created on first use) and marks it for the next
+// join_sides; work put on `*lane` may overlap what follows on the main lane (device bound by the caller).
+libreCudaStatus_t fork_side(LibreCUstream stream, int i, cudaStream_t *lane);
 libreCudaStatus_t host_wait_stream(LibreCUcontext ctx, cudaStream_t s);
 libreCudaStatus_t host_wait_event(LibreCUcontext ctx, cudaEvent_t e);
 bool is_pageable_host(const void *p);

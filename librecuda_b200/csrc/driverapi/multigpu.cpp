@@ -265,15 +265,10 @@ libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, 
                 // the local chunk runs as a kernel on a side lane, beside the engine copies of the main lane
                 LibreCUstream sr = streams[r];
                 LIBRECUDA_ERR_PROPAGATE(bind(sr->ctx));
-                if (sr->side[0] == nullptr) {
-                    LCU_CUDA(cudaStreamCreateWithFlags(&sr->side[0], cudaStreamNonBlocking));
-                    LCU_CUDA(cudaEventCreateWithFlags(&sr->side_done[0], cudaEventDisableTiming));
-                }
-                LCU_CUDA(cudaEventRecord(sr->fork, sr->main));
-                LCU_CUDA(cudaStreamWaitEvent(sr->side[0], sr->fork, 0));
+                cudaStream_t lane = nullptr;
+                LIBRECUDA_ERR_PROPAGATE(fork_side(sr, 0, &lane));
                 LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(recvBufs[r]) + (size_t)r * chunkBytes,
-                                     static_cast<const uint8_t *>(sendBufs[r]) + (size_t)r * chunkBytes, chunkBytes, sr->side[0]));
-                LCU_CUDA(cudaEventRecord(sr->side_done[0], sr->side[0]));
+                                     static_cast<const uint8_t *>(sendBufs[r]) + (size_t)r * chunkBytes, chunkBytes, lane));
             }
             for (int step = 1; step < nDev; ++step) {
                 for (int r = 0; r < nDev; ++r) {
@@ -284,11 +279,7 @@ libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, 
                     LCU_CUDA(cudaMemcpyAsync(d, s, chunkBytes, cudaMemcpyDefault, streams[r]->main));
                 }
             }
-            for (int r = 0; r < nDev; ++r) {
-                LIBRECUDA_ERR_PROPAGATE(bind(streams[r]->ctx));
-                LCU_CUDA(cudaStreamWaitEvent(streams[r]->main, streams[r]->side_done[0], 0));
-            }
-            LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+            LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));  // takes the side lanes in first
         } else if (useNccl == 1) {
             Nccl *n = nccl();
             LIBRECUDA_VALIDATE(n != nullptr, LIBRECUDA_ERROR_NOT_FOUND);
@@ -426,14 +417,7 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
                 LibreCUstream sg = streams[owners[k]];
                 if (off[k + 1] == off[k]) continue;
                 LIBRECUDA_ERR_PROPAGATE(bind(sg->ctx));
-                if (sg->side[0] == nullptr) {
-                    LCU_CUDA(cudaStreamCreateWithFlags(&sg->side[0], cudaStreamNonBlocking));
-                    LCU_CUDA(cudaEventCreateWithFlags(&sg->side_done[0], cudaEventDisableTiming));
-                }
-                push_lane[k] = sg->side[0];
-                LCU_CUDA(cudaEventRecord(sg->fork, sg->main));  // the push lane starts where the stream stands now
-                LCU_CUDA(cudaStreamWaitEvent(push_lane[k], sg->fork, 0));
-                sg->side_dirty[0] = true;  // joined into the main stream below
+                LIBRECUDA_ERR_PROPAGATE(fork_side(sg, 0, &push_lane[k]));  // starts where the stream stands now
             }
         }
         // pieces outermost, devices innermost: every device gets its first work within microseconds of the call
@@ -467,16 +451,8 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
                 }
             }
         }
-        for (int k = 0; k < parts; ++k) {
-            LibreCUstream sg = streams[owners[k]];
-            if (!sg->side_dirty[0]) continue;
-            LIBRECUDA_ERR_PROPAGATE(bind(sg->ctx));
-            LCU_CUDA(cudaEventRecord(sg->side_done[0], sg->side[0]));
-            LCU_CUDA(cudaStreamWaitEvent(sg->main, sg->side_done[0], 0));
-            sg->side_dirty[0] = false;
-        }
         for (cudaEvent_t e : to_destroy) (void)cudaEventDestroy(e);
-        LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+        LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));  // takes the push lanes in first
         return rebind_current();
     });
 }

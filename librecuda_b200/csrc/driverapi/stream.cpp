@@ -63,6 +63,18 @@ libreCudaStatus_t join_sides(LibreCUstream st) {
     LIBRECUDA_SUCCEED();
 }
 
+libreCudaStatus_t fork_side(LibreCUstream st, int i, cudaStream_t *lane) {
+    if (st->side[i] == nullptr) {
+        LCU_CUDA(cudaStreamCreateWithFlags(&st->side[i], cudaStreamNonBlocking));
+        LCU_CUDA(cudaEventCreateWithFlags(&st->side_done[i], cudaEventDisableTiming));
+    }
+    LCU_CUDA(cudaEventRecord(st->fork, st->main));
+    LCU_CUDA(cudaStreamWaitEvent(st->side[i], st->fork, 0));
+    st->side_dirty[i] = true;
+    *lane = st->side[i];
+    LIBRECUDA_SUCCEED();
+}
+
 // Lane an operation runs on: the main stream after a join for ordered operations, a side stream forked
 // from the main stream's current tail for async ones.
 static libreCudaStatus_t pick_lane(LibreCUstream st, bool async, cudaStream_t *lane) {
@@ -73,15 +85,7 @@ static libreCudaStatus_t pick_lane(LibreCUstream st, bool async, cudaStream_t *l
     }
     const int i = st->next_side;
     st->next_side = (i + 1) % kSideLanes;
-    if (st->side[i] == nullptr) {
-        LCU_CUDA(cudaStreamCreateWithFlags(&st->side[i], cudaStreamNonBlocking));
-        LCU_CUDA(cudaEventCreateWithFlags(&st->side_done[i], cudaEventDisableTiming));
-    }
-    LCU_CUDA(cudaEventRecord(st->fork, st->main));
-    LCU_CUDA(cudaStreamWaitEvent(st->side[i], st->fork, 0));
-    st->side_dirty[i] = true;
-    *lane = st->side[i];
-    LIBRECUDA_SUCCEED();
+    return fork_side(st, i, lane);
 }
 
 static libreCudaStatus_t submit(LibreCUstream st, Command &c) {
