@@ -194,8 +194,9 @@ LIBRECUDA_EXPORT libreCudaStatus_t libreCuEventGetTimestamp(uint64_t *pNanosecon
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuDeviceCanAccessPeer(int *pCanAccess, LibreCUdevice device, LibreCUdevice peerDevice);
 // Lets kernels and copies of the current context reach memory allocated in `peerCtx`.  Idempotent.
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuCtxEnablePeerAccess(LibreCUcontext peerCtx, unsigned int flags);
-// Copy between device buffers that may live on different GPUs, executed by the copy kernel on the GPU
-// that owns `stream` (stores to, or loads from, the peer over NVLink).
+// Copy between device buffers that may live on different GPUs: by the copy kernel on the GPU that owns
+// `stream` (stores to, or loads from, the peer over NVLink) or, between two GPUs from 64 MiB up, by the copy
+// engines (the faster form there; lcb_tune("peer_copy_engine", MiB) moves the threshold, 0 = never).
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuMemcpyPeer(void *dstDevice, const void *srcDevice, size_t byteCount, LibreCUstream stream, bool async = false);
 
 // offsetsOut[0..parts] <- boundaries of `parts` contiguous shards of `totalBytes`, every interior
