@@ -165,7 +165,15 @@ extern "C" int lcb_compare_bytes(const void *a, const void *b, size_t bytes, uin
     const int threads = 512;
     size_t need = (nwords + threads - 1) / threads;
     if (need == 0) need = 1;
-    const size_t cap = (size_t)sm_count() * 4;
+    // a grid-stride loop wants exactly one wave: as many CTAs as are resident at once (a partial second wave
+    // starts when the first ends and leaves most of the GPU idle meanwhile)
+    static int resident_per_sm = 0;
+    if (resident_per_sm == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, compare_kernel, threads, 0) != cudaSuccess || n < 1) n = 1;
+        resident_per_sm = n;
+    }
+    const size_t cap = (size_t)sm_count() * (size_t)resident_per_sm;
     const int grid = (int)(need < cap ? need : cap);
     compare_kernel<<<grid, threads, 0, st>>>(reinterpret_cast<const uint64_t *>(pa & ~(uintptr_t)7), (int)(pa & 7) * 8,
                                              reinterpret_cast<const uint64_t *>(pb & ~(uintptr_t)7), (int)(pb & 7) * 8,
