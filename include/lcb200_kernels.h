@@ -95,8 +95,8 @@ size_t lcb_checksum_scratch_bytes(void);
 /* lcb_checksum64 for callers that cannot allocate device memory.  No counterpart in the reference.
  * Same result as lcb_checksum64, but the scratch (one ticket counter + 1024 partial sums, about 8 KiB) is a
  * fixed array compiled into the library, so nothing is allocated here or by the caller: meant for a check
- * that runs when the application's own pool already owns all free HBM, or from code that sits inside a
- * stream capture, where allocating calls are refused.  Limits and rules:
+ * that runs when the application's own pool already owns all free HBM, or from a plug-in whose host forbids
+ * allocating calls.  Limits and rules:
  *   - `bytes` above lcb_checksum64_noalloc_max_bytes() (64 GiB) is rejected with 1 and a line on stderr;
  *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
  *     first call before any stream capture begins;

@@ -210,8 +210,8 @@ extern "C" int lcb_checksum64(const void *src, size_t bytes, uint64_t *scratch, 
 // ---------------------------------------------------------------------------------------------------
 // Some users of this checksum are not in a position to get scratch memory: a verification pass that runs
 // after the application has handed every free byte of HBM to its own pool (the 8 GiB-shard copies this
-// library is built for are usually checked exactly then), or a host that is between cudaStreamBeginCapture
-// and EndCapture, where an allocating call is an error.  For them the ticket counter and the per-CTA
+// library is built for are usually checked exactly then), or a plug-in whose host forbids allocating calls
+// on its threads.  For them the ticket counter and the per-CTA
 // partial sums live in this fixed array inside the library image instead of a caller-supplied buffer.
 // Every GPU that loads the library carries these bytes until the process exits.
 constexpr int kStaticChecksumCtas = 1024;                           // partial-sum slots

@@ -9,7 +9,7 @@
 set -euo pipefail
 here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 root="$(dirname "$here")"
-ref="${1:-${LIBRECUDA_REFERENCE:-/root/reference}}"
+ref="${1:-${LIBRECUDA_REFERENCE:-$root/../reference}}"
 lib="$root/librecuda_b200/lib"
 [ -d "$ref/tests" ] || { echo "no reference checkout at $ref: skipping compat programs"; exit 0; }
 [ -f "$lib/libdriverapi.so" ] || { echo "build libdriverapi.so first (python -m librecuda_b200.build)"; exit 1; }

@@ -2,10 +2,10 @@
 # Builds the oracle's C restatement and, when a reference checkout is available, the reference's own DtoD
 # dispatcher + kernels compiled for the host (oracle/_ref/libref_memcopy.so).  Reference sources are
 # compiled where they lie; nothing is copied.  TEST INFRASTRUCTURE ONLY.
-#   usage: oracle/build_ref.sh [reference-checkout]      (default: $LIBRECUDA_REFERENCE, else the build machine's reference mount)
+#   usage: oracle/build_ref.sh [reference-checkout]      (default: $LIBRECUDA_REFERENCE, else the directory `reference` beside this repository)
 set -euo pipefail
 here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-ref="${1:-${LIBRECUDA_REFERENCE:-/root/reference}}"
+ref="${1:-${LIBRECUDA_REFERENCE:-$(dirname "$here")/../reference}}"
 mkdir -p "$here/_build"
 gcc -O2 -fPIC -shared -pthread -ffp-contract=off -o "$here/_build/liblcb_oracle.so" "$here/lcb_oracle.c"
 echo "built $here/_build/liblcb_oracle.so"

@@ -1,5 +1,5 @@
 """lcb_checksum64_noalloc -- the checksum entry point for callers that cannot allocate device memory (their
-pool already owns the free HBM, or they are inside a stream capture).  It must give exactly what
+pool already owns the free HBM, or their host forbids allocating calls).  It must give exactly what
 lcb_checksum64 gives with caller-provided scratch, call after call, because its built-in scratch array is
 shared by every call and keeps the previous call's contents.  Runs last so that a failure here cannot hide
 any other test's result."""
