@@ -29,6 +29,16 @@ enum lcbCopyPath {
     LCB_COPY_VEC32 = 4, /* 32-byte vector loads+stores; needs (src-dst) % 32 == 0                   */
     LCB_COPY_TMA2 = 5   /* bulk ring with separate load- and store-issuing threads; (src-dst) % 16 == 0 */
 };
+/* Flag that may be OR'ed into the `path` argument of lcb_copy_d2d_ex (LCB_COPY_AUTO, _VEC, _SMALL, _TMA):
+ * the caller vouches that no work submitted earlier to `stream` and possibly still running writes the
+ * SOURCE range.  The kernel then issues its first loads while the previous kernel on the stream is still
+ * draining and only holds its stores back until that kernel has finished.  Without the flag loads wait too.
+ * The libreCu* layer sets it by itself from the command list of a stream. */
+#define LCB_COPY_SRC_STABLE 0x100
+/* Flag for the same argument: launch this copy without programmatic dependent launch, i.e. its CTAs are not
+ * made resident while the previous kernel on the stream still runs.  For callers that drive two streams on
+ * one GPU whose kernels would otherwise take SM slots from each other while they wait. */
+#define LCB_COPY_NO_PDL 0x200
 
 /* Device-to-device copy of `bytes` bytes, any alignment, any size (64-bit offsets).  Buffers must not
  * overlap.  One launch does head, body and tail.
@@ -40,6 +50,13 @@ int lcb_copy_d2d(void *dst, const void *src, size_t bytes, lcbStream stream);
  * exactly that many CTAs, looping over the tiles).  An
  * infeasible request (LCB_COPY_TMA with mutually misaligned pointers) returns 1. */
 int lcb_copy_d2d_ex(void *dst, const void *src, size_t bytes, int path, int ctas, lcbStream stream);
+
+/* Writes into `text` (NUL-terminated, at most text_bytes) which kernel, template arguments, grid and CTA
+ * size lcb_copy_d2d_ex would launch for exactly these arguments on the current device, without launching
+ * anything.  Returns 0, or 1 where lcb_copy_d2d_ex would refuse the request.
+ * ref: the size classes of the reference's dispatcher, driverapi/src/memcopy.cpp:82-107. */
+int lcb_copy_d2d_describe(const void *dst, const void *src, size_t bytes, int path, int ctas, char *text,
+                          size_t text_bytes);
 
 /* Fill `count` elements of 1, 2 or 4 bytes with `value` (low bytes used).  dst must be aligned to the
  * element size.  ref: none -- the reference has no memset (driverapi/include/librecuda.h:37-114);
@@ -75,11 +92,23 @@ int lcb_alltoall_push(void *const *peer_recv, const void *send, size_t chunk_byt
 int lcb_alltoall_pull(void *const *peer_send, void *recv, size_t chunk_bytes, int n_ranks, int rank,
                       lcbStream stream);
 
+/* Copies `bytes` bytes (a multiple of 16; both addresses 16-byte aligned) from ordinary device memory to a
+ * MULTICAST address with multimem stores: NVSwitch writes the data into the memory of every GPU bound to the
+ * multicast object at that offset, while it leaves the storing GPU only once.  mc_dst must be an address of a
+ * multicast mapping (cuMulticastCreate / cuMemMap) that this GPU may access; only stores are issued on it.
+ * ctas = 0: one short CTA per 32 KiB tile; > 0: that many looping CTAs.
+ * ref: none (the reference is single-GPU, librecuda.cpp:61). */
+int lcb_multicast_store(void *mc_dst, const void *src, size_t bytes, int ctas, lcbStream stream);
+
 /* ---- verification helpers that run on the device (used by tests and the benchmark) ------------- */
 
 /* dst[0..bytes) <- the seeded byte stream: 64-bit word i = mix64(seed + (i+1) * 0x9E3779B97F4A7C15),
  * little-endian, mix64 = the splitmix64 finaliser.  dst 8-byte aligned. */
 int lcb_fill_splitmix64(void *dst, size_t bytes, uint64_t seed, lcbStream stream);
+/* The same stream from its 64-bit word `first_word` on: dst[0..bytes) <- bytes [8 * first_word, 8 * first_word
+ * + bytes) of what lcb_fill_splitmix64 would write with this seed, so a window deep inside a multi-GiB
+ * stream can be regenerated without the part before it. */
+int lcb_fill_splitmix64_at(void *dst, size_t bytes, uint64_t seed, uint64_t first_word, lcbStream stream);
 
 /* result[0] <- number of positions where a[i] != b[i]; result[1] <- smallest such i (UINT64_MAX if
  * none).  `result` is device memory for two uint64_t and is overwritten. */
@@ -110,6 +139,10 @@ size_t lcb_checksum64_noalloc_max_bytes(void);
 /* Reads and clears the per-device sticky word that kernels set when a bounded wait (mbarrier) gave
  * up: 0 = no error.  Synchronises the device. */
 int lcb_device_error_word(unsigned int *out);
+/* The same word as last mirrored into host memory by the kernels, read WITHOUT synchronising or clearing:
+ * what a host that has just finished a stream wait consults (libreCuStreamAwait and libreCuEventSynchronize
+ * do).  0 until lcb_preload has run on the device. */
+int lcb_device_error_peek(unsigned int *out);
 
 /* Exercises the give-up path of the kernels' bounded waits without any fault: one thread waits, at most
  * max_tries (1..100000) tries, on a barrier nothing completes, then sets bit 0 of the sticky error word and

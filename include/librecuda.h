@@ -216,6 +216,13 @@ LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAllPull(void *const *peerSendBufs
 // the library's own peer-memory kernels; useNccl == 2 runs them on the copy engines: the all-to-all as G-1
 // rotated peer copies per GPU (the fastest form measured on NVLink 5 when all GPUs exchange at once), the
 // broadcast as a chain root -> next device -> ... pipelined in pieces with one event per piece and hop.
+// libreCuBroadcast also takes useNccl == 3: NVLink multicast.  The root writes its buffer once with multimem
+// stores to a multicast address, NVSwitch delivers a copy into a staging slab of the library on every GPU, and
+// each GPU copies the pieces from its slab into its buffer; nothing is forwarded by a GPU, so the rate does not
+// drop with the number of GPUs.  The buffers themselves can be any device memory (any alignment on the
+// receivers; a root buffer that is not 16-byte aligned, or GPUs without multicast support, take form 2 -- form 0
+// with two GPUs -- instead).  The slabs (512 MiB per GPU by default) are created at the first call for a group
+// of devices and released by libreCuCtxDestroy of any of them, or at exit.
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, size_t chunkBytes, int nDev, const LibreCUstream *streams, int useNccl);
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount, int nDev, const LibreCUstream *streams, int useNccl);
 

@@ -26,6 +26,7 @@ vpp = C.POINTER(C.c_void_p)
 LCB_FUNCTIONS = {
     "lcb_copy_d2d": (i32, [vp, vp, sz, vp]),
     "lcb_copy_d2d_ex": (i32, [vp, vp, sz, i32, i32, vp]),
+    "lcb_copy_d2d_describe": (i32, [vp, vp, sz, i32, i32, C.c_char_p, sz]),
     "lcb_memset_d8": (i32, [vp, C.c_ubyte, sz, vp]),
     "lcb_memset_d16": (i32, [vp, C.c_ushort, sz, vp]),
     "lcb_memset_d32": (i32, [vp, C.c_uint, sz, vp]),
@@ -34,13 +35,16 @@ LCB_FUNCTIONS = {
     "lcb_axpb_f32": (i32, [vp, vp, C.c_float, C.c_float, sz, vp]),
     "lcb_alltoall_push": (i32, [vpp, vp, sz, i32, i32, vp]),
     "lcb_alltoall_pull": (i32, [vpp, vp, sz, i32, i32, vp]),
+    "lcb_multicast_store": (i32, [vp, vp, sz, i32, vp]),
     "lcb_fill_splitmix64": (i32, [vp, sz, u64, vp]),
+    "lcb_fill_splitmix64_at": (i32, [vp, sz, u64, u64, vp]),
     "lcb_compare_bytes": (i32, [vp, vp, sz, vp, vp]),
     "lcb_checksum64": (i32, [vp, sz, vp, vp, vp]),
     "lcb_checksum_scratch_bytes": (sz, []),
     "lcb_checksum64_noalloc": (i32, [vp, sz, vp, vp]),
     "lcb_checksum64_noalloc_max_bytes": (sz, []),
     "lcb_device_error_word": (i32, [C.POINTER(C.c_uint)]),
+    "lcb_device_error_peek": (i32, [C.POINTER(C.c_uint)]),
     "lcb_preload": (i32, []),
     "lcb_selftest_wait_timeout": (i32, [C.c_uint, vp]),
     "lcb_version": (C.c_char_p, []),

@@ -5,6 +5,7 @@
 #include <cstring>
 
 #include "internal.h"
+#include "multicast.h"
 
 // ---- status variables (data symbols, reference driverapi/src/librecuda_status.cpp:7-11) -----------------
 extern "C" {
@@ -239,8 +240,12 @@ libreCudaStatus_t libreCuCtxCreate_v2(LibreCUcontext *pCtx, int flags, LibreCUde
         ctx->peers.insert(device->ordinal);
         LCU_CUDA(cudaSetDevice(device->ordinal));
         LCU_CUDA(cudaFree(nullptr));  // forces creation of the primary context
-        LCU_CUDA(cudaEventCreate(&ctx->epoch));
-        LCU_CUDA(cudaEventRecord(ctx->epoch, nullptr));
+        LibreCUcontext_::Epoch first;
+        LCU_CUDA(cudaEventCreate(&first.ev));
+        LCU_CUDA(cudaEventRecord(first.ev, nullptr));
+        first.host_ms = steady_ms();
+        ctx->epochs.push_back(first);
+        ctx->epoch_base_ns.push_back(0);
         LCU_LCB(lcb_preload());  // the reference loads its copy kernels here as well (librecuda.cpp:622)
         globals().current = ctx.get();  // reference: librecuda.cpp:619
         *pCtx = ctx.release();
@@ -251,9 +256,11 @@ libreCudaStatus_t libreCuCtxCreate_v2(LibreCUcontext *pCtx, int flags, LibreCUde
 libreCudaStatus_t libreCuCtxDestroy(LibreCUcontext ctx) {
     LIBRECUDA_VALIDATE(ctx != nullptr, LIBRECUDA_ERROR_INVALID_CONTEXT);
     if (globals().current == ctx) globals().current = nullptr;
+    mc_release_all();  // multicast slabs bound on this GPU go before its context does (re-created on demand)
     if (cudaSetDevice(ctx->device->ordinal) == cudaSuccess) {
         (void)cudaDeviceSynchronize();
-        if (ctx->epoch) (void)cudaEventDestroy(ctx->epoch);
+        for (auto &ep : ctx->epochs)
+            if (ep.ev) (void)cudaEventDestroy(ep.ev);
     }
     (void)cudaGetLastError();
     delete ctx;

@@ -16,6 +16,7 @@
 #include <string>
 #include <vector>
 
+#include "host_logic.h"
 #include "lcb200_kernels.h"
 #include "librecuda.h"
 
@@ -86,9 +87,10 @@ const DriverTable *driver();
 struct Allocation {
     void *raw;        // pointer returned by the CUDA allocator (what is freed)
     size_t size;      // usable bytes from the aligned pointer
-    int device;
+    int device;       // the GPU whose memory it is (for an IPC mapping: the exporting process's GPU)
     bool mapped;      // host-dereferenceable (managed)
     bool ipc;         // opened from another process's handle
+    int opener = -1;  // IPC mappings: the device that was current when the handle was opened (bound again to close it)
 };
 
 struct Globals {
@@ -122,7 +124,16 @@ struct LibreCUdevice_ {
 struct LibreCUcontext_ {
     LibreCUdevice device = nullptr;
     int flags = 0;
-    cudaEvent_t epoch = nullptr;  // recorded at creation; event timestamps are measured from it
+    // Event timestamps count from epochs[0], recorded at creation.  A new epoch is recorded in front of an
+    // event when the newest one is older than a couple of seconds, so that the float distance CUDA reports
+    // between an event and its epoch keeps sub-microsecond resolution however old the context is.
+    struct Epoch {
+        cudaEvent_t ev = nullptr;
+        uint64_t host_ms = 0;  // host clock when it was recorded
+    };
+    std::vector<Epoch> epochs;
+    std::vector<uint64_t> epoch_base_ns;  // offset of epochs[k] from epochs[0], valid below epochs_resolved
+    size_t epochs_resolved = 0;
     std::set<int> peers;          // device ordinals whose memory this context may access
 };
 
@@ -148,6 +159,7 @@ struct LibreCUEvent_ {
     LibreCUcontext ctx = nullptr;
     cudaEvent_t ev = nullptr;
     int device = -1;
+    size_t epoch_idx = 0;  // the context epoch that was newest when the event was submitted
 };
 
 namespace lcu {
@@ -176,6 +188,7 @@ struct Command {
 };
 
 constexpr int kSideLanes = 8;
+constexpr uint64_t kEpochRollMs = 2000;             // a new timestamp epoch once the newest is this old
 constexpr int kStageSlots = 4;                      // pinned bounce slots per stream for pageable host copies
 constexpr size_t kStageBytes = (size_t)8 << 20;    // bytes per slot
 constexpr size_t kStageMinBytes = (size_t)1 << 20; // smaller pageable copies go straight to the runtime
@@ -190,6 +203,7 @@ struct LibreCUstream_ {
     bool side_dirty[lcu::kSideLanes] = {};
     cudaEvent_t fork = nullptr;
     int next_side = 0;
+    lcu::WriteLog main_writes;  // what library kernels possibly still running on `main` write
     std::vector<lcu::Command> pending;
     void *stage[lcu::kStageSlots] = {};
     cudaEvent_t stage_done[lcu::kStageSlots] = {};

@@ -16,6 +16,7 @@
 #include <cstring>
 
 #include "internal.h"
+#include "multicast.h"
 
 using namespace lcu;
 
@@ -220,6 +221,7 @@ libreCudaStatus_t cross_join(int nDev, const LibreCUstream *streams) {
     for (int r = 0; r < nDev; ++r) {
         LIBRECUDA_ERR_PROPAGATE(bind(streams[r]->ctx));
         LIBRECUDA_ERR_PROPAGATE(join_sides(streams[r]));
+        streams[r]->main_writes.add_unknown();  // the collectives' kernels write buffers this record does not follow
         LCU_CUDA(cudaEventCreateWithFlags(&done[r], cudaEventDisableTiming));
         LCU_CUDA(cudaEventRecord(done[r], streams[r]->main));
     }
@@ -259,8 +261,14 @@ libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, 
         if (chunkBytes == 0) LIBRECUDA_SUCCEED();
         if (useNccl == 2) {
             // copy engines: rank r sends chunk (r+s) mod n to rank (r+s) mod n at step s, so that at every step
-            // each GPU receives from exactly one sender; its own chunk goes through the local copy kernel
+            // each GPU receives from exactly one sender; its own chunk goes through the local copy kernel.
+            // Two engine copies that land on one GPU at the same time, or leave one GPU at the same time, fall to
+            // about half the rate each AND idle another port meanwhile (measured: 500 GB/s per GPU instead of
+            // 700-750 with 2-3 concurrent copies per GPU), so the schedule must stay in lock-step: the receiver of
+            // rank r's step s was served by rank r+1 at step s-1, and rank r's copy waits for that one (one event
+            // per copy).  Nothing then depends on the ranks running at the same speed.
             LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+            std::vector<cudaEvent_t> landed((size_t)nDev, nullptr), landed_prev((size_t)nDev, nullptr);
             for (int r = 0; r < nDev; ++r) {
                 // the local chunk runs as a kernel on a side lane, beside the engine copies of the main lane
                 LibreCUstream sr = streams[r];
@@ -271,14 +279,25 @@ libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, 
                                      static_cast<const uint8_t *>(sendBufs[r]) + (size_t)r * chunkBytes, chunkBytes, lane));
             }
             for (int step = 1; step < nDev; ++step) {
+                landed_prev.swap(landed);
                 for (int r = 0; r < nDev; ++r) {
                     const int j = (r + step) % nDev;
                     LIBRECUDA_ERR_PROPAGATE(bind(streams[r]->ctx));
                     uint8_t *d = static_cast<uint8_t *>(recvBufs[j]) + (size_t)r * chunkBytes;
                     const uint8_t *s = static_cast<const uint8_t *>(sendBufs[r]) + (size_t)j * chunkBytes;
+                    if (step > 1 && nDev > 2) LCU_CUDA(cudaStreamWaitEvent(streams[r]->main, landed_prev[(size_t)((r + 1) % nDev)], 0));
                     LCU_CUDA(cudaMemcpyAsync(d, s, chunkBytes, cudaMemcpyDefault, streams[r]->main));
+                    if (step + 1 < nDev && nDev > 2) {
+                        LCU_CUDA(cudaEventCreateWithFlags(&landed[(size_t)r], cudaEventDisableTiming));
+                        LCU_CUDA(cudaEventRecord(landed[(size_t)r], streams[r]->main));
+                    }
                 }
+                for (cudaEvent_t e : landed_prev)
+                    if (e != nullptr) (void)cudaEventDestroy(e);  // released once the waits have consumed it
+                std::fill(landed_prev.begin(), landed_prev.end(), nullptr);
             }
+            for (cudaEvent_t e : landed)
+                if (e != nullptr) (void)cudaEventDestroy(e);
             LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));  // takes the side lanes in first
         } else if (useNccl == 1) {
             Nccl *n = nccl();
@@ -314,6 +333,115 @@ libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, 
     });
 }
 
+namespace {
+
+// Copy-engine chain over bytes [lo, hi) of the buffers: root -> d1 -> d2 -> ... in device order, piece by piece,
+// on lanes[k] of device k.  The lane of chain member h pushes piece p to member h+1 as soon as member h-1 has
+// delivered it (one event per piece and hop), so every GPU receives and sends at the engines' rate at once.
+// Time = bytes / rate + pieces * c + (members - 2) * piece / rate, where c, the cost of one dependent peer copy,
+// measured 7-12 us (4 GPUs, 4 GiB: 571 / 623 / 671 / 686 GB/s with 16 / 32 / 64 / 128 MiB pieces; alternating
+// the pieces over two lanes per member changed nothing, so the cost sits in the engine, not in the lane).  The
+// piece that minimises it is sqrt(bytes * c * rate / (members - 2)), c * rate = 7.75 MB.
+libreCudaStatus_t bcast_chain(void *const *bufs, int root, size_t lo, size_t hi, int nDev, const LibreCUstream *streams,
+                              const std::vector<cudaStream_t> &lanes) {
+    if (hi <= lo) LIBRECUDA_SUCCEED();
+    const size_t bytes = hi - lo;
+    std::vector<int> chain;
+    for (int k = 0; k < nDev; ++k) chain.push_back((root + k) % nDev);
+    size_t piece = bytes;
+    if (nDev > 2) {
+        const int piece_mib = lcb_tune_get("bcast_engine_piece_mib");
+        if (piece_mib > 0) {
+            piece = (size_t)piece_mib << 20;
+        } else {
+            const double best = std::sqrt((double)bytes * 7.75e6 / (double)(nDev - 2));
+            piece = ((size_t)(best / 1048576.0) + 1) << 20;
+        }
+    }
+    std::vector<cudaEvent_t> arrived(nDev, nullptr);  // arrived[h]: the current piece has reached member h
+    for (size_t p = lo; p < hi; p += piece) {
+        const size_t n = hi - p < piece ? hi - p : piece;
+        for (int h = 0; h + 1 < nDev; ++h) {
+            const int dev = chain[h];
+            LIBRECUDA_ERR_PROPAGATE(bind(streams[dev]->ctx));
+            if (h > 0) {
+                LCU_CUDA(cudaStreamWaitEvent(lanes[dev], arrived[h], 0));
+                (void)cudaEventDestroy(arrived[h]);  // released once the wait has consumed it
+                arrived[h] = nullptr;
+            }
+            LCU_CUDA(cudaMemcpyAsync(static_cast<uint8_t *>(bufs[chain[h + 1]]) + p,
+                                     static_cast<const uint8_t *>(bufs[dev]) + p, n, cudaMemcpyDefault, lanes[dev]));
+            if (h + 2 < nDev) {
+                LCU_CUDA(cudaEventCreateWithFlags(&arrived[h + 1], cudaEventDisableTiming));
+                LCU_CUDA(cudaEventRecord(arrived[h + 1], lanes[dev]));
+            }
+        }
+    }
+    LIBRECUDA_SUCCEED();
+}
+
+// Multicast through NVSwitch over bytes [lo, hi) (lo a multiple of 16; the caller has checked that the root
+// buffer is 16-byte aligned).  The root's kernel reads its buffer once and writes it with multimem stores to a
+// multicast address: every byte leaves the root's port once and the switch puts a copy into a staging slab on
+// every GPU of the group; each GPU then moves the piece from its own slab into the caller's buffer with a local
+// copy (HBM speed, a small fraction of the link time).  Nobody forwards anything, so the rate does not fall
+// with the number of GPUs: 550 / 543 GB/s at 2 / 4 GPUs, whatever the kernel's shape (16 ... 1184 CTAs, 1-8
+// vectors per thread, weak or relaxed stores) -- the fabric's rate for multicast writes from one GPU, below the
+// 690-780 GB/s of the copy-engine chain there, which is why this form is not the default recommendation.  The
+// slabs are a ring of `slots` pieces; the root reuses a slot once every GPU has copied the piece out of it (one
+// event per GPU and slot), and a GPU starts its local copy when the root's kernel for that piece has finished.
+libreCudaStatus_t bcast_multicast(void *const *bufs, int root, size_t lo, size_t hi, int nDev, const LibreCUstream *streams,
+                                  const std::vector<cudaStream_t> &lanes, const McWindow *win, size_t piece, int slots) {
+    if (hi <= lo) LIBRECUDA_SUCCEED();
+    const uint8_t *src = static_cast<const uint8_t *>(bufs[root]);
+    uint8_t *mc = static_cast<uint8_t *>(win->mc);
+    std::vector<cudaEvent_t> filled((size_t)slots, nullptr);
+    std::vector<cudaEvent_t> consumed((size_t)slots * (size_t)nDev, nullptr);
+    std::vector<cudaEvent_t> retired;
+    const size_t body_end = lo + ((hi - lo) & ~(size_t)15);  // multimem stores move whole 16-byte vectors
+    const int ctas = lcb_tune_get("bcast_mc_ctas");
+    size_t idx = 0;
+    for (size_t p = lo; p < body_end; p += piece, ++idx) {
+        const size_t n = body_end - p < piece ? body_end - p : piece;
+        const size_t slot = idx % (size_t)slots;
+        LIBRECUDA_ERR_PROPAGATE(bind(streams[root]->ctx));
+        for (int g = 0; g < nDev; ++g) {  // the slot is free again once every GPU has emptied it
+            cudaEvent_t &c = consumed[slot * (size_t)nDev + (size_t)g];
+            if (c == nullptr) continue;
+            LCU_CUDA(cudaStreamWaitEvent(lanes[root], c, 0));
+            retired.push_back(c);
+            c = nullptr;
+        }
+        LCU_LCB(lcb_multicast_store(mc + slot * piece, src + p, n, ctas, lanes[root]));
+        if (filled[slot] != nullptr) retired.push_back(filled[slot]);
+        LCU_CUDA(cudaEventCreateWithFlags(&filled[slot], cudaEventDisableTiming));
+        LCU_CUDA(cudaEventRecord(filled[slot], lanes[root]));
+        for (int g = 0; g < nDev; ++g) {
+            if (g == root) continue;
+            LIBRECUDA_ERR_PROPAGATE(bind(streams[g]->ctx));
+            LCU_CUDA(cudaStreamWaitEvent(lanes[g], filled[slot], 0));
+            LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[g]) + p, static_cast<const uint8_t *>(win->local[g]) + slot * piece, n,
+                                 lanes[g]));
+            cudaEvent_t &c = consumed[slot * (size_t)nDev + (size_t)g];
+            LCU_CUDA(cudaEventCreateWithFlags(&c, cudaEventDisableTiming));
+            LCU_CUDA(cudaEventRecord(c, lanes[g]));
+        }
+    }
+    if (body_end < hi) {  // the last few bytes: plain stores from the root into every buffer
+        LIBRECUDA_ERR_PROPAGATE(bind(streams[root]->ctx));
+        for (int g = 0; g < nDev; ++g)
+            if (g != root) LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[g]) + body_end, src + body_end, hi - body_end, lanes[root]));
+    }
+    for (cudaEvent_t e : filled)
+        if (e != nullptr) (void)cudaEventDestroy(e);
+    for (cudaEvent_t e : consumed)
+        if (e != nullptr) (void)cudaEventDestroy(e);
+    for (cudaEvent_t e : retired) (void)cudaEventDestroy(e);
+    LIBRECUDA_SUCCEED();
+}
+
+}  // namespace
+
 libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount, int nDev, const LibreCUstream *streams,
                                    int useNccl) {
     return lcu_guarded([&]() -> libreCudaStatus_t {
@@ -322,50 +450,38 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
         LIBRECUDA_ERR_PROPAGATE(check_group(nDev, streams, &devs));
         LIBRECUDA_VALIDATE(root >= 0 && root < nDev, LIBRECUDA_ERROR_INVALID_VALUE);
         for (int r = 0; r < nDev; ++r) LIBRECUDA_VALIDATE(bufs[r] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-        LIBRECUDA_VALIDATE(useNccl >= 0 && useNccl <= 2, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(useNccl >= 0 && useNccl <= 3, LIBRECUDA_ERROR_INVALID_VALUE);
         if (useNccl != 1) LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, bufs));
         for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(commence(streams[r]));
         if (byteCount == 0 || nDev == 1) LIBRECUDA_SUCCEED();
+        std::vector<cudaStream_t> mains((size_t)nDev);
+        for (int r = 0; r < nDev; ++r) mains[(size_t)r] = streams[r]->main;
+        if (useNccl == 3) {
+            // Multicast (see bcast_multicast).  Needs multicast support on every GPU and a 16-byte aligned root
+            // buffer; otherwise the call falls back to the copy-engine chain (form 2; form 0 with two GPUs).
+            // Running the chain beside it on a share of the bytes does not add the two rates up: the mix measured
+            // 410-505 GB/s at 4 GPUs for every split, below either path alone (543 and 689).
+            const int piece_mib = lcb_tune_get("bcast_mc_piece_mib") > 0 ? lcb_tune_get("bcast_mc_piece_mib") : 256;
+            const int slots = lcb_tune_get("bcast_mc_slots") >= 2 ? lcb_tune_get("bcast_mc_slots") : 2;
+            const size_t piece = (size_t)piece_mib << 20;
+            const McWindow *win = nullptr;
+            int rc = -1;
+            if ((reinterpret_cast<uintptr_t>(bufs[root]) & 15) == 0) rc = mc_window_acquire(devs.data(), nDev, piece * (size_t)slots, &win);
+            if (rc > 0) {
+                LIBRECUDA_DEBUG("multicast window could not be created (CUresult " << rc << "); using the copy-engine chain");
+                rc = -1;
+            }
+            if (rc == 0) {
+                LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+                LIBRECUDA_ERR_PROPAGATE(bcast_multicast(bufs, root, 0, byteCount, nDev, streams, mains, win, piece, slots));
+                LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+                return rebind_current();
+            }
+            useNccl = nDev == 2 ? 0 : 2;
+        }
         if (useNccl == 2) {
-            // Copy-engine chain: root -> d1 -> d2 -> ... in device order, piece by piece.  The stream of chain
-            // member h pushes piece p to member h+1 as soon as member h-1 has delivered it (one event per piece
-            // and hop), so every GPU receives and sends at the engines' rate at once.  Time = bytes / rate
-            // + pieces * c + (members - 2) * piece / rate, where c, the cost of one dependent peer copy, measured
-            // 7-12 us (4 GPUs, 4 GiB: 571 / 623 / 671 / 686 GB/s with 16 / 32 / 64 / 128 MiB pieces; alternating
-            // the pieces over two lanes per member changed nothing, so the cost sits in the engine, not in the
-            // lane).  The piece that minimises it is sqrt(bytes * c * rate / (members - 2)), c * rate = 7.75 MB.
-            std::vector<int> chain;
-            for (int k = 0; k < nDev; ++k) chain.push_back((root + k) % nDev);
-            size_t piece = byteCount;
-            if (nDev > 2) {
-                const int piece_mib = lcb_tune_get("bcast_engine_piece_mib");
-                if (piece_mib > 0) {
-                    piece = (size_t)piece_mib << 20;
-                } else {
-                    const double best = std::sqrt((double)byteCount * 7.75e6 / (double)(nDev - 2));
-                    piece = ((size_t)(best / 1048576.0) + 1) << 20;
-                }
-            }
             LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
-            std::vector<cudaEvent_t> arrived(nDev, nullptr);  // arrived[h]: the current piece has reached member h
-            for (size_t p = 0; p < byteCount; p += piece) {
-                const size_t n = byteCount - p < piece ? byteCount - p : piece;
-                for (int h = 0; h + 1 < nDev; ++h) {
-                    LibreCUstream sh = streams[chain[h]];
-                    LIBRECUDA_ERR_PROPAGATE(bind(sh->ctx));
-                    if (h > 0) {
-                        LCU_CUDA(cudaStreamWaitEvent(sh->main, arrived[h], 0));
-                        (void)cudaEventDestroy(arrived[h]);  // released once the wait has consumed it
-                        arrived[h] = nullptr;
-                    }
-                    LCU_CUDA(cudaMemcpyAsync(static_cast<uint8_t *>(bufs[chain[h + 1]]) + p,
-                                             static_cast<const uint8_t *>(bufs[chain[h]]) + p, n, cudaMemcpyDefault, sh->main));
-                    if (h + 2 < nDev) {
-                        LCU_CUDA(cudaEventCreateWithFlags(&arrived[h + 1], cudaEventDisableTiming));
-                        LCU_CUDA(cudaEventRecord(arrived[h + 1], sh->main));
-                    }
-                }
-            }
+            LIBRECUDA_ERR_PROPAGATE(bcast_chain(bufs, root, 0, byteCount, nDev, streams, mains));
             LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
             return rebind_current();
         }
@@ -403,12 +519,8 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
         const int pull_ctas = lcb_tune_get("bcast_pull_ctas") > 0 ? lcb_tune_get("bcast_pull_ctas") : 74;
         // Programmatic dependent launch parks the next kernel's CTAs on the SMs while they wait; good for one
         // stream of back-to-back copies, bad here, where two lanes of every device must share the SMs (measured:
-        // 8.7 ms with it, 7.2 ms without at 4 GPUs).  Off for the launches of this call.
-        struct PdlOff {
-            int saved = lcb_tune_get("pdl");
-            PdlOff() { lcb_tune("pdl", 0); }
-            ~PdlOff() { lcb_tune("pdl", saved); }
-        } pdl_off;
+        // 8.7 ms with it, 7.2 ms without at 4 GPUs).  Every launch of this call asks for a plain launch.
+        constexpr int kPlain = LCB_COPY_NO_PDL;
         const size_t kPiece = parts > 1 ? ((size_t)piece_mib << 20) : ~(size_t)0;
         std::vector<cudaEvent_t> to_destroy;
         std::vector<cudaStream_t> push_lane(parts, nullptr);
@@ -437,8 +549,8 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
                 // The pull shares the root's port with all the other devices, so it is slow by construction; with a
                 // full grid its waiting CTAs would fill every SM and starve the forwarding kernels of this device
                 // (measured: the broadcast took twice as long).  74 looping CTAs carry the pull's share comfortably.
-                if (push_lane[k] == nullptr) LCU_LCB(lcb_copy_d2d(mine + p, src + p, n, sg->main));
-                else LCU_LCB(lcb_copy_d2d_ex(mine + p, src + p, n, LCB_COPY_VEC, pull_ctas, sg->main));
+                if (push_lane[k] == nullptr) LCU_LCB(lcb_copy_d2d_ex(mine + p, src + p, n, LCB_COPY_AUTO | kPlain, 0, sg->main));
+                else LCU_LCB(lcb_copy_d2d_ex(mine + p, src + p, n, LCB_COPY_VEC | kPlain, pull_ctas, sg->main));
                 if (push_lane[k] == nullptr) continue;
                 cudaEvent_t landed;
                 LCU_CUDA(cudaEventCreateWithFlags(&landed, cudaEventDisableTiming));
@@ -447,7 +559,7 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
                 LCU_CUDA(cudaStreamWaitEvent(push_lane[k], landed, 0));
                 for (int step = 1; step < parts; ++step) {  // rotate the targets so the stores spread over the peers
                     const int q = owners[(k + step) % parts];
-                    LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[q]) + p, mine + p, n, push_lane[k]));
+                    LCU_LCB(lcb_copy_d2d_ex(static_cast<uint8_t *>(bufs[q]) + p, mine + p, n, LCB_COPY_AUTO | kPlain, 0, push_lane[k]));
                 }
             }
         }
@@ -489,15 +601,19 @@ libreCudaStatus_t libreCuIpcOpenMemHandle(void **pDevicePointer, const void *han
     LCU_CUDA(cudaIpcOpenMemHandle(&raw, h, cudaIpcMemLazyEnablePeerAccess));
     void *p = static_cast<uint8_t *>(raw) + offset;
     // opening with cudaIpcMemLazyEnablePeerAccess gave this context access to the exporting GPU's memory
+    const int opener = globals().current->device->ordinal;
+    int owner = opener;
     cudaPointerAttributes attr{};
     if (cudaPointerGetAttributes(&attr, raw) == cudaSuccess && attr.type == cudaMemoryTypeDevice) {
         globals().current->peers.insert(attr.device);
+        owner = attr.device;
     } else {
         (void)cudaGetLastError();
     }
     // size unknown on this side: register the page that holds the pointer so classification sees device memory;
-    // the CUDA driver answers for the rest of the range
-    globals().allocations[reinterpret_cast<uintptr_t>(p)] = Allocation{raw, 4096, globals().current->device->ordinal, false, true};
+    // the CUDA driver answers for the rest of the range.  The recorded owner is the exporting GPU, which is also
+    // what the driver reports beyond this page, so every offset into the mapping has the same owner.
+    globals().allocations[reinterpret_cast<uintptr_t>(p)] = Allocation{raw, 4096, owner, false, true, opener};
     *pDevicePointer = p;
     LIBRECUDA_SUCCEED();
 }
@@ -507,7 +623,7 @@ libreCudaStatus_t libreCuIpcCloseMemHandle(void *devicePointer) {
     auto &allocs = globals().allocations;
     auto it = allocs.find(reinterpret_cast<uintptr_t>(devicePointer));
     LIBRECUDA_VALIDATE(it != allocs.end() && it->second.ipc, LIBRECUDA_ERROR_INVALID_VALUE);
-    LCU_CUDA(cudaSetDevice(it->second.device));
+    LCU_CUDA(cudaSetDevice(it->second.opener >= 0 ? it->second.opener : it->second.device));
     void *raw = it->second.raw;
     allocs.erase(it);
     LCU_CUDA(cudaIpcCloseMemHandle(raw));

@@ -28,21 +28,58 @@ libreCudaStatus_t record(LibreCUstream stream, Command &&cmd) {
     LIBRECUDA_SUCCEED();
 }
 
+// Limit of a host wait in milliseconds, from LIBRECUDA_WAIT_TIMEOUT_MS (unset or 0: wait for ever, like the
+// reference's signalWaitCpu, cmdqueue.cpp:346-352).  With a limit, a wait that runs out returns NOT_READY and
+// the work stays submitted: the caller may wait again.
+static uint64_t wait_limit_ms() {
+    static const uint64_t limit = [] {
+        const char *e = std::getenv("LIBRECUDA_WAIT_TIMEOUT_MS");
+        const long long v = e ? std::atoll(e) : 0;
+        return v > 0 ? (uint64_t)v : (uint64_t)0;
+    }();
+    return limit;
+}
+
+// A kernel of this library that gave up a bounded wait leaves its copy incomplete and raises the device's
+// sticky error word; the stream itself finishes without a CUDA error.  Checked after every host wait, so a
+// program written for the reference (which only ever looks at the status of Await) cannot take a partial
+// copy for a finished one.  The word is reported once and cleared.
+static libreCudaStatus_t check_device_error_word() {
+    unsigned int w = 0;
+    if (lcb_device_error_peek(&w) != 0 || w == 0) LIBRECUDA_SUCCEED();
+    unsigned int cleared = 0;
+    (void)lcb_device_error_word(&cleared);
+    LIBRECUDA_DEBUG("device error word " << (w | cleared) << ": a kernel of this library gave up a bounded wait; its operation is incomplete");
+    LIBRECUDA_FAIL(LIBRECUDA_ERROR_UNKNOWN);
+}
+
 // Host-side wait in the style chosen at context creation (reference cmdqueue.cpp:337-355).
 template <typename QueryFn, typename BlockFn>
 static libreCudaStatus_t host_wait(LibreCUcontext ctx, QueryFn query, BlockFn block) {
     const int flags = ctx ? ctx->flags : 0;
-    if (flags & CU_CTX_SCHED_BLOCKING_SYNC) {
+    const uint64_t limit = wait_limit_ms();
+    if ((flags & CU_CTX_SCHED_BLOCKING_SYNC) && limit == 0) {
         LCU_CUDA(block());
-        LIBRECUDA_SUCCEED();
+        return check_device_error_word();
     }
-    const bool yield = !(flags & CU_CTX_SCHED_SPIN) && (flags & CU_CTX_SCHED_YIELD);
-    for (;;) {
-        cudaError_t q = query();
-        if (q == cudaSuccess) LIBRECUDA_SUCCEED();
-        if (q != cudaErrorNotReady) LCU_CUDA(q);
-        if (yield) std::this_thread::yield();
+    // blocking contexts with a limit poll and yield: a blocking CUDA wait cannot be given a deadline
+    const bool yield = (flags & CU_CTX_SCHED_BLOCKING_SYNC) || (!(flags & CU_CTX_SCHED_SPIN) && (flags & CU_CTX_SCHED_YIELD));
+    cudaError_t failure = cudaSuccess;
+    const WaitOutcome out = poll_until(
+        [&] {
+            const cudaError_t q = query();
+            if (q == cudaSuccess) return PollResult::Done;
+            if (q == cudaErrorNotReady) return PollResult::Pending;
+            failure = q;
+            return PollResult::Failed;
+        },
+        steady_ms, limit, yield);
+    if (out == WaitOutcome::Failed) LCU_CUDA(failure);
+    if (out == WaitOutcome::TimedOut) {
+        LIBRECUDA_DEBUG("host wait gave up after " << limit << " ms (LIBRECUDA_WAIT_TIMEOUT_MS)");
+        LIBRECUDA_FAIL(LIBRECUDA_ERROR_NOT_READY);
     }
+    return check_device_error_word();
 }
 
 libreCudaStatus_t host_wait_stream(LibreCUcontext ctx, cudaStream_t s) {
@@ -91,12 +128,23 @@ static libreCudaStatus_t pick_lane(LibreCUstream st, bool async, cudaStream_t *l
 static libreCudaStatus_t submit(LibreCUstream st, Command &c) {
     cudaStream_t lane = nullptr;
     switch (c.kind) {
-        case Command::CopyKernel:
+        case Command::CopyKernel: {
             LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
-            LCU_LCB(lcb_copy_d2d(c.dst, c.src, c.bytes, lane));
+            // An ordered copy whose source no library kernel still in flight on the main lane writes may load
+            // before the previous kernel has drained (its stores still wait).  Async copies run on side lanes
+            // that start behind an event, where there is nothing to overlap with.
+            int path = LCB_COPY_AUTO;
+            if (!c.async) {
+                if (!st->main_writes.may_be_written(c.src, c.bytes)) path |= LCB_COPY_SRC_STABLE;
+                st->main_writes.add(c.dst, c.bytes);
+            }
+            LCU_LCB(lcb_copy_d2d_ex(c.dst, c.src, c.bytes, path, 0, lane));
             break;
+        }
         case Command::CopyEngine:
             LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
+            // a copy-engine transfer starts after, and the next kernel after it starts behind, everything before it
+            if (!c.async) st->main_writes.clear();
             if (c.bytes >= kStageMinBytes && c.copy_kind == cudaMemcpyHostToDevice && is_pageable_host(c.src)) {
                 LIBRECUDA_ERR_PROPAGATE(staged_h2d(st, lane, c.dst, c.src, c.bytes));
             } else if (c.bytes >= kStageMinBytes && c.copy_kind == cudaMemcpyDeviceToHost && is_pageable_host(c.dst)) {
@@ -107,18 +155,24 @@ static libreCudaStatus_t submit(LibreCUstream st, Command &c) {
             break;
         case Command::Memset:
             LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
+            if (!c.async) st->main_writes.add(c.dst, c.bytes);
             LCU_LCB(lcb_memset_ex(c.dst, c.value, c.elem, c.bytes / (size_t)c.elem, 0, 0, lane));
             break;
         case Command::AllToAllPush:
             LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
+            if (!c.async) st->main_writes.add_unknown();  // writes into every peer's buffer
             LCU_LCB(lcb_alltoall_push(c.peers.data(), c.src, c.bytes, (int)c.peers.size(), c.rank, lane));
             break;
         case Command::AllToAllPull:
             LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
+            if (!c.async) st->main_writes.add(c.dst, c.bytes * c.peers.size());
             LCU_LCB(lcb_alltoall_pull(c.peers.data(), c.dst, c.bytes, (int)c.peers.size(), c.rank, lane));
             break;
         case Command::Launch: {
             LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
+            // a user kernel is launched without programmatic serialization: it starts after, and whatever follows
+            // it starts behind, everything submitted before
+            if (!c.async) st->main_writes.clear();
             LibreCUFunction f = c.fn;
             std::vector<void *> argv(f->param_size.size());
             for (size_t i = 0; i < argv.size(); ++i) argv[i] = c.params.data() + f->param_offset[i];
@@ -136,6 +190,19 @@ static libreCudaStatus_t submit(LibreCUstream st, Command &c) {
             if (e->ev == nullptr) {
                 LCU_CUDA(cudaEventCreate(&e->ev));
                 e->device = st->ctx->device->ordinal;
+            }
+            {   // a fresh epoch in front of the event when the newest one is getting old (see LibreCUcontext_)
+                LibreCUcontext ctx = st->ctx;
+                const uint64_t now = steady_ms();
+                if (now - ctx->epochs.back().host_ms >= kEpochRollMs) {
+                    LibreCUcontext_::Epoch ep;
+                    LCU_CUDA(cudaEventCreate(&ep.ev));
+                    LCU_CUDA(cudaEventRecord(ep.ev, st->main));
+                    ep.host_ms = now;
+                    ctx->epochs.push_back(ep);
+                    ctx->epoch_base_ns.push_back(0);
+                }
+                e->epoch_idx = ctx->epochs.size() - 1;
             }
             LCU_CUDA(cudaEventRecord(e->ev, st->main));
             e->state = LibreCUEvent_::Submitted;
@@ -233,10 +300,11 @@ libreCudaStatus_t libreCuStreamAwait(LibreCUstream stream) {
     LIBRECUDA_VALIDATE(stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
     LIBRECUDA_ERR_PROPAGATE(bind(stream->ctx));
     LIBRECUDA_ERR_PROPAGATE(join_sides(stream));
-    LIBRECUDA_ERR_PROPAGATE(host_wait_stream(stream->ctx, stream->main));
+    const libreCudaStatus_t waited = host_wait_stream(stream->ctx, stream->main);
+    if (waited == LIBRECUDA_SUCCESS) stream->main_writes.clear();  // nothing is in flight any more
     LibreCUcontext cur = globals().current;
     if (cur != nullptr && cur != stream->ctx) LIBRECUDA_ERR_PROPAGATE(bind(cur));
-    LIBRECUDA_SUCCEED();
+    return waited;
 }
 
 libreCudaStatus_t libreCuStreamGetNativeHandle(void **pNativeStreamOut, LibreCUstream stream) {
@@ -270,7 +338,7 @@ static libreCudaStatus_t record_copy(void *dst, const void *src, size_t n, Libre
         // (measured: 4 GiB cut into 16 ... 2048 back-to-back copies), a kernel launch about 2.5.  The engines
         // win from about 44 MB up: a cross-device copy of 64 MiB and more goes to them (knob, in MiB; 0 = never).
         const int od = owner_device(dst), os = owner_device(src);
-        const int engine_mib = lcb_tune_get("peer_copy_engine");
+        const int engine_mib = (od >= 0 && os >= 0 && od != os) ? lcb_tune_get("peer_copy_engine") : 0;
         if (od >= 0 && os >= 0 && od != os && engine_mib > 0 && n >= ((size_t)engine_mib << 20)) {
             c.kind = Command::CopyEngine;
             c.copy_kind = cudaMemcpyDefault;
@@ -391,7 +459,11 @@ libreCudaStatus_t libreCuEventSynchronize(LibreCUEvent event) {
     LIBRECUDA_VALIDATE(event->state != LibreCUEvent_::Never, LIBRECUDA_ERROR_INVALID_VALUE);  // reference librecuda.cpp:1633
     // recorded but its stream never commenced: the reference would spin forever (cmdqueue.cpp:928-940)
     LIBRECUDA_VALIDATE(event->state == LibreCUEvent_::Submitted, LIBRECUDA_ERROR_NOT_READY);
-    return host_wait_event(event->ctx, event->ev);
+    LIBRECUDA_ERR_PROPAGATE(bind(event->ctx));  // the error word consulted after the wait is the event's device's
+    const libreCudaStatus_t waited = host_wait_event(event->ctx, event->ev);
+    LibreCUcontext cur = globals().current;
+    if (cur != nullptr && cur != event->ctx) LIBRECUDA_ERR_PROPAGATE(bind(cur));
+    return waited;
 }
 
 libreCudaStatus_t libreCuEventQuery(LibreCUEvent event) {
@@ -424,15 +496,28 @@ libreCudaStatus_t libreCuEventGetTimestamp(uint64_t *pNanosecondsOut, LibreCUEve
     LIBRECUDA_VALIDATE(event != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
     LIBRECUDA_VALIDATE(event->state != LibreCUEvent_::Never, LIBRECUDA_ERROR_INVALID_VALUE);
     if (event->state != LibreCUEvent_::Submitted) LIBRECUDA_FAIL(LIBRECUDA_ERROR_NOT_READY);
-    float ms = 0.f;
-    cudaError_t e = cudaEventElapsedTime(&ms, event->ctx->epoch, event->ev);
-    if (e == cudaErrorNotReady) {
+    LibreCUcontext ctx = event->ctx;
+    // offsets of the epochs up to the event's own, as far as the GPU has reached them
+    (void)resolve_epochs(ctx->epoch_base_ns, ctx->epochs_resolved, event->epoch_idx, [&](size_t a, size_t b, float *ms) {
+        const cudaError_t e = cudaEventElapsedTime(ms, ctx->epochs[a].ev, ctx->epochs[b].ev);
+        if (e != cudaSuccess) (void)cudaGetLastError();
+        return e == cudaSuccess;
+    });
+    // measure from the newest resolved epoch at or before the event's (an epoch recorded on another stream may
+    // not have been reached yet although the event has: fall back to an older one)
+    size_t k = event->epoch_idx < ctx->epochs_resolved ? event->epoch_idx : ctx->epochs_resolved - 1;
+    for (;; --k) {
+        float ms = 0.f;
+        const cudaError_t e = cudaEventElapsedTime(&ms, ctx->epochs[k].ev, event->ev);
+        if (e == cudaSuccess) {
+            const int64_t t = (int64_t)ctx->epoch_base_ns[k] + (int64_t)((double)ms * 1.0e6);
+            *pNanosecondsOut = t > 0 ? (uint64_t)t : 0;
+            LIBRECUDA_SUCCEED();
+        }
         (void)cudaGetLastError();
-        LIBRECUDA_FAIL(LIBRECUDA_ERROR_NOT_READY);
+        if (e != cudaErrorNotReady) LCU_CUDA(e);
+        if (k == 0) LIBRECUDA_FAIL(LIBRECUDA_ERROR_NOT_READY);
     }
-    LCU_CUDA(e);
-    *pNanosecondsOut = (uint64_t)((double)ms * 1.0e6);
-    LIBRECUDA_SUCCEED();
 }
 
 libreCudaStatus_t libreCuEventDestroy(LibreCUEvent event) {

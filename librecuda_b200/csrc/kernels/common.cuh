@@ -17,7 +17,7 @@ struct Tuning {
     int copy_vec_unroll;    // 16-byte vectors in flight per thread
     int copy_vec_ctas_sm;   // 0: one short CTA per tile; > 0: persistent grid of this many CTAs per SM
     int copy_cache_mode;    // 0: ld.cs/st.cs   1: default caching   2: L1::no_allocate
-    int tma_chunk;          // bytes per bulk copy
+    int tma_chunk;          // bytes per bulk copy; 0: chunk, stages and lookahead chosen by the copy's size
     int tma_stages;         // ring depth
     int tma_lookahead;      // loads in flight ahead of the store
     int tma_ctas_sm;        // 0: one chunk per CTA; > 0: persistent ring, this many CTAs per SM
@@ -46,11 +46,15 @@ struct Tuning {
     int bcast_piece_mib;     // own broadcast: MiB per pipelined piece
     int bcast_pull_ctas;     // own broadcast: CTAs of the kernel that pulls from the root (it must not fill the GPU)
     int bcast_engine_piece_mib;  // copy-engine chain broadcast: MiB per piece, 0 = chosen from the size and the number of GPUs
+    int bcast_mc_piece_mib;      // multicast broadcast: MiB per piece
+    int bcast_mc_slots;          // multicast broadcast: pieces in the staging ring of every GPU
+    int bcast_mc_ctas;           // multicast broadcast: looping CTAs of the root's store kernel (0: one short CTA per tile)
 };
 Tuning &tuning();
 
 int preload_copy_kernels();  // force-load the default copy / fill kernels on the current device
 int preload_fill_kernels();
+int setup_error_mirror();    // host-mapped mirror of the sticky error word for the current device
 int sm_count();            // SMs of the current device (cached per device)
 int check_launch();        // cudaGetLastError() as int
 
@@ -64,6 +68,23 @@ int check_launch();        // cudaGetLastError() as int
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Launches made by this thread while a NoPdlScope lives go without the programmatic-serialization attribute
+// (LCB_COPY_NO_PDL): for callers that run two lanes on one GPU and do not want parked CTAs of a dependent
+// kernel to hold SM slots.  Thread-local, so another thread's launches are unaffected.
+inline int &no_pdl_depth() {
+    static thread_local int depth = 0;
+    return depth;
+}
+struct NoPdlScope {
+    bool on;
+    explicit NoPdlScope(bool enable) : on(enable) {
+        if (on) ++no_pdl_depth();
+    }
+    ~NoPdlScope() {
+        if (on) --no_pdl_depth();
+    }
+};
+
 template <typename... KArgs, typename... Args>
 inline int launch_kernel(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t st,
                          Args... args) {
@@ -73,7 +94,7 @@ inline int launch_kernel(void (*kernel)(KArgs...), unsigned grid, unsigned block
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
-    if (tuning().pdl) {
+    if (tuning().pdl && no_pdl_depth() == 0) {
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
@@ -89,8 +110,11 @@ inline int launch_kernel(void (*kernel)(KArgs...), unsigned grid, unsigned block
 // ---------------------------------------------------------------------------------------------
 // streaming 16-byte accesses
 // ---------------------------------------------------------------------------------------------
+// MODE 0: .cs both ways   1: default caching   2: L1::no_allocate both ways
+//      3: loads as 2, stores with an L2 evict_first policy   4: loads and stores with that policy
+// (`pol` is only read by modes 3 and 4: the value of policy_evict_first(), created once per thread)
 template <int MODE>
-__device__ __forceinline__ uint4 ld_stream(const uint4 *p) {
+__device__ __forceinline__ uint4 ld_stream(const uint4 *p, uint64_t pol = 0) {
     uint4 v;
     if (MODE == 0) {
         asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -98,6 +122,9 @@ __device__ __forceinline__ uint4 ld_stream(const uint4 *p) {
     } else if (MODE == 1) {
         asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];"
                      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    } else if (MODE == 4) {
+        asm volatile("ld.global.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(pol));
     } else {
         asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
@@ -106,13 +133,16 @@ __device__ __forceinline__ uint4 ld_stream(const uint4 *p) {
 }
 
 template <int MODE>
-__device__ __forceinline__ void st_stream(uint4 *p, uint4 v) {
+__device__ __forceinline__ void st_stream(uint4 *p, uint4 v, uint64_t pol = 0) {
     if (MODE == 0) {
         asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};"
                      :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
     } else if (MODE == 1) {
         asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};"
                      :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+    } else if (MODE >= 3) {
+        asm volatile("st.global.L1::no_allocate.L2::cache_hint.v4.u32 [%0], {%1,%2,%3,%4}, %5;"
+                     :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "l"(pol) : "memory");
     } else {
         asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};"
                      :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");

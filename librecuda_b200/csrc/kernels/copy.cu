@@ -20,6 +20,8 @@
 //                       usable with a peer GPU's memory on either side.
 //  * alltoall_kernel     one launch that moves every chunk of an all-to-all between this GPU and all its
 //                       peers (the copy fused with the exchange), by remote loads (pull) or stores (push).
+#include <cstdio>
+
 #include "common.cuh"
 #include "lcb200_kernels.h"
 
@@ -27,6 +29,18 @@ namespace lcb {
 
 // Sticky per-device error word, read and cleared by lcb_device_error_word().
 __device__ unsigned int g_error_word = 0;
+// Host-mapped mirror of that word (set up per device by setup_error_mirror): a kernel that gives up a wait
+// also raises the bit there, so the host can look at it after any stream wait without a device round trip.
+__device__ unsigned int *g_error_mirror = nullptr;
+
+__device__ __forceinline__ void raise_error(unsigned int bits) {
+    atomicOr(&g_error_word, bits);
+    unsigned int *m = g_error_mirror;
+    if (m != nullptr) {
+        atomicOr_system(m, bits);
+        __threadfence_system();
+    }
+}
 
 // ---------------------------------------------------------------------------------------------
 // vector path
@@ -63,31 +77,44 @@ __device__ __forceinline__ void copy_edges(const Edges &e, int t) {
 // SW < 0: src and dst congruent mod 16 (srcv is the source body itself).
 // SW in 0..3: srcv is the source body rounded DOWN to 16 bytes; output vector j is bytes
 // [16 j + s, 16 j + s + 16) of the srcv stream with s = 4 SW + sb8 / 8, 1 <= s <= 15.
+// early != 0: the caller vouches that nothing still running on the stream writes the source, so the first
+// tile's loads are issued BEFORE the wait for the previous kernel (they fly while that kernel drains); every
+// store still comes after the wait.
 template <int SW, int U, int MODE>
 __global__ void __launch_bounds__(512) copy_vec_kernel(uint4 *__restrict__ dstv, const uint4 *__restrict__ srcv,
-                                                       size_t nvec, int sb8, Edges e) {
+                                                       size_t nvec, int sb8, Edges e, int early) {
     const int lane = threadIdx.x & 31;
     const size_t warps_total = (size_t)gridDim.x * (blockDim.x >> 5);
     const size_t gwarp = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     constexpr size_t TILE = (size_t)U * 32;  // vectors per warp per iteration
     const size_t ntiles = (nvec + TILE - 1) / TILE;
+    uint64_t pol = 0;
+    if (MODE >= 3) pol = policy_evict_first();
 
     pdl_launch_dependents();
-    pdl_wait();
-    if (blockIdx.x == 0) copy_edges(e, threadIdx.x);
+    bool waited = false;
+    if (!early) {
+        pdl_wait();
+        waited = true;
+        if (blockIdx.x == 0) copy_edges(e, threadIdx.x);
+    }
 
     for (size_t t = gwarp; t < ntiles; t += warps_total) {
         const size_t base = t * TILE;
         uint4 v[U];
         if (base + TILE <= nvec) {  // full tile: no guards
 #pragma unroll
-            for (int u = 0; u < U; ++u) v[u] = ld_stream<MODE>(srcv + base + u * 32 + lane);
+            for (int u = 0; u < U; ++u) v[u] = ld_stream<MODE>(srcv + base + u * 32 + lane, pol);
+            uint4 extra = make_uint4(0, 0, 0, 0);
+            if (SW >= 0 && lane == 0) extra = ld_stream<MODE>(srcv + base + TILE, pol);
+            if (!waited) {
+                pdl_wait();
+                waited = true;
+            }
             if (SW < 0) {
 #pragma unroll
-                for (int u = 0; u < U; ++u) st_stream<MODE>(dstv + base + u * 32 + lane, v[u]);
+                for (int u = 0; u < U; ++u) st_stream<MODE>(dstv + base + u * 32 + lane, v[u], pol);
             } else {
-                uint4 extra = make_uint4(0, 0, 0, 0);
-                if (lane == 0) extra = ld_stream<MODE>(srcv + base + TILE);
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     // every lane needs the vector one to its right; lane 31's neighbour is lane 0's next row
@@ -99,7 +126,7 @@ __global__ void __launch_bounds__(512) copy_vec_kernel(uint4 *__restrict__ dstv,
                     nxt.y = __shfl_sync(0xffffffffu, give.y, from);
                     nxt.z = __shfl_sync(0xffffffffu, give.z, from);
                     nxt.w = __shfl_sync(0xffffffffu, give.w, from);
-                    st_stream<MODE>(dstv + base + u * 32 + lane, realign<(SW < 0 ? 0 : SW)>(v[u], nxt, sb8));
+                    st_stream<MODE>(dstv + base + u * 32 + lane, realign<(SW < 0 ? 0 : SW)>(v[u], nxt, sb8), pol);
                 }
             }
         } else {  // last, partial tile
@@ -108,17 +135,21 @@ __global__ void __launch_bounds__(512) copy_vec_kernel(uint4 *__restrict__ dstv,
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const size_t j = base + u * 32 + lane;
-                v[u] = (j < src_limit) ? ld_stream<MODE>(srcv + j) : make_uint4(0, 0, 0, 0);
+                v[u] = (j < src_limit) ? ld_stream<MODE>(srcv + j, pol) : make_uint4(0, 0, 0, 0);
+            }
+            uint4 extra = make_uint4(0, 0, 0, 0);
+            if (SW >= 0 && lane == 0 && base + TILE < src_limit) extra = ld_stream<MODE>(srcv + base + TILE, pol);
+            if (!waited) {
+                pdl_wait();
+                waited = true;
             }
             if (SW < 0) {
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     const size_t j = base + u * 32 + lane;
-                    if (j < nvec) st_stream<MODE>(dstv + j, v[u]);
+                    if (j < nvec) st_stream<MODE>(dstv + j, v[u], pol);
                 }
             } else {
-                uint4 extra = make_uint4(0, 0, 0, 0);
-                if (lane == 0 && base + TILE < src_limit) extra = ld_stream<MODE>(srcv + base + TILE);
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     uint4 give = v[u];
@@ -130,10 +161,15 @@ __global__ void __launch_bounds__(512) copy_vec_kernel(uint4 *__restrict__ dstv,
                     nxt.z = __shfl_sync(0xffffffffu, give.z, from);
                     nxt.w = __shfl_sync(0xffffffffu, give.w, from);
                     const size_t j = base + u * 32 + lane;
-                    if (j < nvec) st_stream<MODE>(dstv + j, realign<(SW < 0 ? 0 : SW)>(v[u], nxt, sb8));
+                    if (j < nvec) st_stream<MODE>(dstv + j, realign<(SW < 0 ? 0 : SW)>(v[u], nxt, sb8), pol);
                 }
             }
         }
+    }
+    if (early) {  // every thread passes the wait before it exits, so completion of this kernel implies completion
+                  // of the one before it (the next kernel's wait relies on that); the edge bytes are stores
+        if (!waited) pdl_wait();
+        if (blockIdx.x == 0) copy_edges(e, threadIdx.x);
     }
 }
 
@@ -202,7 +238,7 @@ __global__ void __launch_bounds__(512) copy_vec32_kernel(uint8_t *__restrict__ d
 // shared memory, i.e. at most S-L younger store groups may still be pending.
 template <int S, int L, bool HINT>
 __global__ void __launch_bounds__(32) copy_tma_kernel(uint8_t *__restrict__ dst, const uint8_t *__restrict__ src,
-                                                      size_t body, uint32_t chunk, Edges e) {
+                                                      size_t body, uint32_t chunk, Edges e, int early) {
     extern __shared__ __align__(128) uint8_t smem[];
     static_assert(L >= 1 && L < S, "need at least one stage of slack between loads and stores");
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)S * chunk);
@@ -212,8 +248,11 @@ __global__ void __launch_bounds__(32) copy_tma_kernel(uint8_t *__restrict__ dst,
         for (int s = 0; s < S; ++s) mbar_init(smem_addr(bars) + 8 * s, 1);
         mbar_init_fence();
     }
-    pdl_wait();
+    // early != 0 (nothing still running on the stream writes the source): the first loads are issued before
+    // the wait for the previous kernel; stores, edge bytes included, always come after it
+    if (!early) pdl_wait();
     if (blockIdx.x == 0 && threadIdx.x != 0) {
+        if (early) pdl_wait();
         // lanes 1..15 -> head bytes, lanes 16..31 -> tail bytes
         const int t = threadIdx.x;
         if (t < 16) {
@@ -229,7 +268,10 @@ __global__ void __launch_bounds__(32) copy_tma_kernel(uint8_t *__restrict__ dst,
     // The issuing thread is the only one running, so everything in its loop is kept incremental: no division,
     // no 64-bit multiply, stage and parity carried along.
     const size_t nchunks = (body + chunk - 1) / chunk;
-    if ((size_t)blockIdx.x >= nchunks) return;
+    if ((size_t)blockIdx.x >= nchunks) {
+        if (early) pdl_wait();
+        return;
+    }
     const uint32_t n_my = (uint32_t)((nchunks - blockIdx.x + gridDim.x - 1) / gridDim.x);
     const size_t stride = (size_t)gridDim.x * chunk;
     const uint32_t smem_base = smem_addr(smem);
@@ -252,6 +294,7 @@ __global__ void __launch_bounds__(32) copy_tma_kernel(uint8_t *__restrict__ dst,
         ++issued;
     };
     while (issued < (uint32_t)L && issued < n_my) issue_load();
+    if (early) pdl_wait();
 
     // store cursor
     size_t st_off = (size_t)blockIdx.x * chunk;
@@ -274,7 +317,7 @@ __global__ void __launch_bounds__(32) copy_tma_kernel(uint8_t *__restrict__ dst,
         }
     }
     if (!ok) {
-        atomicOr(&g_error_word, kErrMbarrierTimeout);
+        raise_error(kErrMbarrierTimeout);
         // loads already issued still target our shared memory: give each one more bounded wait
         for (uint32_t j = k; j < issued; ++j) mbar_wait_bounded(bar_base + 8 * (j % S), (j / S) & 1);
     }
@@ -334,7 +377,7 @@ __global__ void __launch_bounds__(64) copy_tma2_kernel(uint8_t *__restrict__ dst
                 parity ^= 1;
             }
         }
-        if (!ok) atomicOr(&g_error_word, kErrMbarrierTimeout);
+        if (!ok) raise_error(kErrMbarrierTimeout);
         return;
     }
     // ---- storer
@@ -355,7 +398,7 @@ __global__ void __launch_bounds__(64) copy_tma2_kernel(uint8_t *__restrict__ dst
             rel_stage = (rel_stage + 1 == S) ? 0 : rel_stage + 1;
         }
     }
-    if (!ok) atomicOr(&g_error_word, kErrMbarrierTimeout);
+    if (!ok) raise_error(kErrMbarrierTimeout);
     bulk_wait_all();
 }
 
@@ -412,6 +455,11 @@ __global__ void __launch_bounds__(512) alltoall_kernel(PeerPtrs peers, uint4 *__
 // ---------------------------------------------------------------------------------------------
 namespace {
 
+// What a launcher decided; filled instead of launching when the caller only asks for the plan.
+struct Plan {
+    char text[160];
+};
+
 struct Split {
     Edges e;
     uint4 *dstv;
@@ -440,27 +488,31 @@ Split split_copy(void *dst, const void *src, size_t bytes) {
 
 template <int SW, int U>
 int launch_vec_mode(int mode, int grid, int threads, cudaStream_t st, uint4 *dstv, const uint4 *srcv, size_t nvec,
-                    int sb8, const Edges &e) {
+                    int sb8, const Edges &e, int early) {
     const size_t pad = (size_t)tuning().copy_vec_smem_pad;
+    if constexpr (SW < 0) {  // the L2-policy modes exist for congruent pointers only
+        if (mode == 3) return launch_kernel(copy_vec_kernel<SW, U, 3>, grid, threads, pad, st, dstv, srcv, nvec, sb8, e, early);
+        if (mode == 4) return launch_kernel(copy_vec_kernel<SW, U, 4>, grid, threads, pad, st, dstv, srcv, nvec, sb8, e, early);
+    }
     switch (mode) {
-        case 1: return launch_kernel(copy_vec_kernel<SW, U, 1>, grid, threads, pad, st, dstv, srcv, nvec, sb8, e);
-        case 2: return launch_kernel(copy_vec_kernel<SW, U, 2>, grid, threads, pad, st, dstv, srcv, nvec, sb8, e);
-        default: return launch_kernel(copy_vec_kernel<SW, U, 0>, grid, threads, pad, st, dstv, srcv, nvec, sb8, e);
+        case 0: return launch_kernel(copy_vec_kernel<SW, U, 0>, grid, threads, pad, st, dstv, srcv, nvec, sb8, e, early);
+        case 1: return launch_kernel(copy_vec_kernel<SW, U, 1>, grid, threads, pad, st, dstv, srcv, nvec, sb8, e, early);
+        default: return launch_kernel(copy_vec_kernel<SW, U, 2>, grid, threads, pad, st, dstv, srcv, nvec, sb8, e, early);
     }
 }
 
 template <int SW>
 int launch_vec_unroll(int unroll, int mode, int grid, int threads, cudaStream_t st, uint4 *dstv, const uint4 *srcv,
-                      size_t nvec, int sb8, const Edges &e) {
+                      size_t nvec, int sb8, const Edges &e, int early) {
     switch (unroll) {
-        case 1: return launch_vec_mode<SW, 1>(mode, grid, threads, st, dstv, srcv, nvec, sb8, e);
-        case 2: return launch_vec_mode<SW, 2>(mode, grid, threads, st, dstv, srcv, nvec, sb8, e);
-        case 8: return launch_vec_mode<SW, 8>(mode, grid, threads, st, dstv, srcv, nvec, sb8, e);
-        default: return launch_vec_mode<SW, 4>(mode, grid, threads, st, dstv, srcv, nvec, sb8, e);
+        case 1: return launch_vec_mode<SW, 1>(mode, grid, threads, st, dstv, srcv, nvec, sb8, e, early);
+        case 2: return launch_vec_mode<SW, 2>(mode, grid, threads, st, dstv, srcv, nvec, sb8, e, early);
+        case 8: return launch_vec_mode<SW, 8>(mode, grid, threads, st, dstv, srcv, nvec, sb8, e, early);
+        default: return launch_vec_mode<SW, 4>(mode, grid, threads, st, dstv, srcv, nvec, sb8, e, early);
     }
 }
 
-int launch_vec(const Split &sp, int ctas, bool small, cudaStream_t st) {
+int launch_vec(const Split &sp, int ctas, bool small, cudaStream_t st, int early, Plan *plan) {
     const Tuning &tu = tuning();
     const bool realign = (reinterpret_cast<uintptr_t>(sp.src_body) & 15) != 0;
     // Launch shape.  Measured on B200: one SHORT CTA per tile -- a grid as large as the tile count, scheduled by
@@ -502,13 +554,21 @@ int launch_vec(const Split &sp, int ctas, bool small, cudaStream_t st) {
     const int s = (int)(sa & 15);
     const uint4 *srcv = reinterpret_cast<const uint4 *>(sa - s);
     const int sb8 = (s & 3) * 8;
-    const int mode = tu.copy_cache_mode;
-    if (s == 0) return launch_vec_unroll<-1>(unroll, mode, grid, threads, st, sp.dstv, srcv, sp.nvec, 0, sp.e);
+    int mode = tu.copy_cache_mode;
+    if (s != 0 && mode > 2) mode = 2;
+    if (unroll != 1 && unroll != 2 && unroll != 8) unroll = 4;
+    if (plan != nullptr) {
+        snprintf(plan->text, sizeof(plan->text), "copy_vec_kernel<%d,%d,%d>, %d CTAs x %d threads, %zu bytes per CTA%s%s",
+                 s == 0 ? -1 : (s >> 2), unroll, mode, grid, threads, per_cta * 16, (size_t)grid < need ? ", looping" : "",
+                 early ? ", loads before the stream wait" : "");
+        return 0;
+    }
+    if (s == 0) return launch_vec_unroll<-1>(unroll, mode, grid, threads, st, sp.dstv, srcv, sp.nvec, 0, sp.e, early);
     switch (s >> 2) {
-        case 0: return launch_vec_unroll<0>(unroll, mode, grid, threads, st, sp.dstv, srcv, sp.nvec, sb8, sp.e);
-        case 1: return launch_vec_unroll<1>(unroll, mode, grid, threads, st, sp.dstv, srcv, sp.nvec, sb8, sp.e);
-        case 2: return launch_vec_unroll<2>(unroll, mode, grid, threads, st, sp.dstv, srcv, sp.nvec, sb8, sp.e);
-        default: return launch_vec_unroll<3>(unroll, mode, grid, threads, st, sp.dstv, srcv, sp.nvec, sb8, sp.e);
+        case 0: return launch_vec_unroll<0>(unroll, mode, grid, threads, st, sp.dstv, srcv, sp.nvec, sb8, sp.e, early);
+        case 1: return launch_vec_unroll<1>(unroll, mode, grid, threads, st, sp.dstv, srcv, sp.nvec, sb8, sp.e, early);
+        case 2: return launch_vec_unroll<2>(unroll, mode, grid, threads, st, sp.dstv, srcv, sp.nvec, sb8, sp.e, early);
+        default: return launch_vec_unroll<3>(unroll, mode, grid, threads, st, sp.dstv, srcv, sp.nvec, sb8, sp.e, early);
     }
 }
 
@@ -539,28 +599,49 @@ int launch_vec32(void *dst, const void *src, size_t bytes, int ctas, cudaStream_
 
 template <int S, int L>
 int launch_tma_cfg(bool hint, int grid, size_t smem, cudaStream_t st, uint8_t *d, const uint8_t *s, size_t body,
-                   uint32_t chunk, const Edges &e) {
+                   uint32_t chunk, const Edges &e, int early) {
     const size_t total = smem + (size_t)tuning().tma_smem_pad;
-    if (hint) return launch_kernel(copy_tma_kernel<S, L, true>, grid, 32, total, st, d, s, body, chunk, e);
-    return launch_kernel(copy_tma_kernel<S, L, false>, grid, 32, total, st, d, s, body, chunk, e);
+    if (hint) return launch_kernel(copy_tma_kernel<S, L, true>, grid, 32, total, st, d, s, body, chunk, e, early);
+    return launch_kernel(copy_tma_kernel<S, L, false>, grid, 32, total, st, d, s, body, chunk, e, early);
 }
 
-int launch_tma(const Split &sp, int ctas, cudaStream_t st) {
+int launch_tma(const Split &sp, int ctas, cudaStream_t st, int early, Plan *plan) {
     const Tuning &tu = tuning();
+    const size_t body = sp.nvec * 16;
     uint32_t chunk = (uint32_t)tu.tma_chunk;
+    int S = tu.tma_stages, L = tu.tma_lookahead;
+    if (chunk == 0) {
+        // chosen by size (every CTA moves ONE chunk; measured on B200 with the loads issued ahead of the stream
+        // wait): below 512 MiB an 8 KiB chunk with three stages' worth of shared memory reserved, which caps
+        // residency at 9 CTAs per SM (6.86 / 6.96 TB/s at 128 / 256 MiB against 6.85 / 6.95 for one 32 KiB
+        // chunk and 6.67 / 6.81 for the vector kernel); from 512 MiB up a 32 KiB chunk (6.97-6.98 TB/s)
+        if (body < ((size_t)512 << 20)) {
+            chunk = 8192;
+            S = 3;
+            L = 2;
+        } else {
+            chunk = 32768;
+            S = 2;
+            L = 1;
+        }
+    }
     if (chunk < 1024 || chunk > 65536 || (chunk & 127)) return 1;
-    const int S = tu.tma_stages, L = tu.tma_lookahead;
     const size_t smem = (size_t)S * chunk + 8 * S;
     if (smem > 227 * 1024) return 1;
-    const size_t body = sp.nvec * 16;
     const size_t nchunks = (body + chunk - 1) / chunk;
     // tma_ctas_sm == 0: one chunk per CTA (short CTAs, 7.0 TB/s); > 0: persistent ring of that many CTAs per SM
     size_t cap = ctas > 0 ? (size_t)ctas : tu.tma_ctas_sm > 0 ? (size_t)sm_count() * tu.tma_ctas_sm : ((size_t)1 << 30);
     int grid = (int)(nchunks < cap ? (nchunks ? nchunks : 1) : cap);
     uint8_t *d = reinterpret_cast<uint8_t *>(sp.dstv);
     const bool hint = tu.tma_cache_hint != 0;
+    if (plan != nullptr) {
+        snprintf(plan->text, sizeof(plan->text), "copy_tma_kernel<%d,%d,%d>, %d CTAs x 32 threads, %u-byte bulk copies%s%s", S, L,
+                 hint ? 1 : 0, grid, chunk, (size_t)grid < nchunks ? ", persistent ring" : ", one per CTA",
+                 early ? ", loads before the stream wait" : "");
+        return 0;
+    }
 #define LCB_TMA_CFG(S_, L_) \
-    if (S == S_ && L == L_) return launch_tma_cfg<S_, L_>(hint, grid, smem, st, d, sp.src_body, body, chunk, sp.e)
+    if (S == S_ && L == L_) return launch_tma_cfg<S_, L_>(hint, grid, smem, st, d, sp.src_body, body, chunk, sp.e, early)
     LCB_TMA_CFG(2, 1);
     LCB_TMA_CFG(3, 2);
     LCB_TMA_CFG(4, 2);
@@ -627,7 +708,7 @@ __global__ void wait_timeout_selftest_kernel(uint32_t max_tries) {
     if (threadIdx.x != 0) return;
     mbar_init(smem_addr(&bar), 1);
     mbar_init_fence();
-    if (!mbar_wait_bounded(smem_addr(&bar), 0, max_tries)) atomicOr(&g_error_word, kErrMbarrierTimeout);
+    if (!mbar_wait_bounded(smem_addr(&bar), 0, max_tries)) raise_error(kErrMbarrierTimeout);
 }
 }  // namespace lcb
 
@@ -655,11 +736,15 @@ int preload_copy_kernels() {
 }
 }  // namespace lcb
 
-extern "C" int lcb_copy_d2d_ex(void *dst, const void *src, size_t bytes, int path, int ctas, lcbStream stream) {
-    using namespace lcb;
-    if (bytes == 0) return 0;
+namespace lcb {
+namespace {
+// Shared by the launcher and the plan query, so the description cannot drift from what is launched.
+int copy_dispatch(void *dst, const void *src, size_t bytes, int path_and_flags, int ctas, cudaStream_t st, Plan *plan) {
     if (dst == nullptr || src == nullptr || ctas < 0) return 1;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int early = (path_and_flags & LCB_COPY_SRC_STABLE) ? 1 : 0;
+    int path = path_and_flags & 0xff;
+    if ((path_and_flags & ~(0xff | LCB_COPY_SRC_STABLE | LCB_COPY_NO_PDL)) != 0) return 1;
+    NoPdlScope no_pdl((path_and_flags & LCB_COPY_NO_PDL) != 0);
     const Split sp = split_copy(dst, src, bytes);
     const bool mutual = ((reinterpret_cast<uintptr_t>(dst) ^ reinterpret_cast<uintptr_t>(src)) & 15) == 0;
     if (path == LCB_COPY_AUTO) {
@@ -669,23 +754,40 @@ extern "C" int lcb_copy_d2d_ex(void *dst, const void *src, size_t bytes, int pat
         else path = LCB_COPY_VEC;
     }
     switch (path) {
-        case LCB_COPY_VEC: return launch_vec(sp, ctas, false, st);
-        case LCB_COPY_SMALL: return launch_vec(sp, ctas, true, st);
+        case LCB_COPY_VEC: return launch_vec(sp, ctas, false, st, early, plan);
+        case LCB_COPY_SMALL: return launch_vec(sp, ctas, true, st, early, plan);
         case LCB_COPY_TMA:
             if (!mutual) return 1;
-            return launch_tma(sp, ctas, st);
+            return launch_tma(sp, ctas, st, early, plan);
         case LCB_COPY_TMA2:
-            if (!mutual) return 1;
+            if (!mutual || plan != nullptr) return 1;
             return launch_tma2(sp, ctas, st);
         case LCB_COPY_VEC32:
-            if (((reinterpret_cast<uintptr_t>(dst) ^ reinterpret_cast<uintptr_t>(src)) & 31) != 0) return 1;
+            if (((reinterpret_cast<uintptr_t>(dst) ^ reinterpret_cast<uintptr_t>(src)) & 31) != 0 || plan != nullptr) return 1;
             return launch_vec32(dst, src, bytes, ctas, st);
         default: return 1;
     }
 }
+}  // namespace
+}  // namespace lcb
+
+extern "C" int lcb_copy_d2d_ex(void *dst, const void *src, size_t bytes, int path, int ctas, lcbStream stream) {
+    if (bytes == 0) return 0;
+    return lcb::copy_dispatch(dst, src, bytes, path, ctas, static_cast<cudaStream_t>(stream), nullptr);
+}
 
 extern "C" int lcb_copy_d2d(void *dst, const void *src, size_t bytes, lcbStream stream) {
     return lcb_copy_d2d_ex(dst, src, bytes, LCB_COPY_AUTO, 0, stream);
+}
+
+extern "C" int lcb_copy_d2d_describe(const void *dst, const void *src, size_t bytes, int path, int ctas, char *text,
+                                     size_t text_bytes) {
+    if (text == nullptr || text_bytes == 0 || bytes == 0) return 1;
+    lcb::Plan plan{};
+    const int rc = lcb::copy_dispatch(const_cast<void *>(dst), src, bytes, path, ctas, nullptr, &plan);
+    if (rc != 0) return rc;
+    snprintf(text, text_bytes, "%s", plan.text);
+    return 0;
 }
 
 namespace lcb {
@@ -730,6 +832,44 @@ extern "C" int lcb_alltoall_pull(void *const *peer_send, void *recv, size_t chun
     return lcb::launch_alltoall(true, peer_send, recv, chunk_bytes, n_ranks, rank, stream);
 }
 
+namespace lcb {
+namespace {
+unsigned int *g_mirror_host[64] = {};  // per device ordinal: the host side of the mirror word
+}
+
+// Gives the current device its host-mapped mirror word (once per device).  Called from lcb_preload.
+int setup_error_mirror() {
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return (int)err;
+    if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    if (g_mirror_host[dev] != nullptr) return 0;
+    unsigned int *h = nullptr, *d = nullptr;
+    err = cudaHostAlloc(reinterpret_cast<void **>(&h), sizeof(unsigned int), cudaHostAllocMapped | cudaHostAllocPortable);
+    if (err != cudaSuccess) return (int)err;
+    *h = 0;
+    err = cudaHostGetDevicePointer(reinterpret_cast<void **>(&d), h, 0);
+    if (err == cudaSuccess) err = cudaMemcpyToSymbol(g_error_mirror, &d, sizeof(d));
+    if (err != cudaSuccess) {
+        (void)cudaFreeHost(h);
+        return (int)err;
+    }
+    g_mirror_host[dev] = h;
+    return 0;
+}
+}  // namespace lcb
+
+extern "C" int lcb_device_error_peek(unsigned int *out) {
+    if (out == nullptr) return 1;
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return (int)err;
+    if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    const volatile unsigned int *h = lcb::g_mirror_host[dev];
+    *out = h ? *h : 0u;
+    return 0;
+}
+
 extern "C" int lcb_device_error_word(unsigned int *out) {
     if (out == nullptr) return 1;
     cudaError_t err = cudaDeviceSynchronize();
@@ -742,6 +882,9 @@ extern "C" int lcb_device_error_word(unsigned int *out) {
         err = cudaMemcpyToSymbol(lcb::g_error_word, &zero, sizeof(zero));
         if (err != cudaSuccess) return (int)err;
     }
+    int dev = -1;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && lcb::g_mirror_host[dev] != nullptr)
+        *lcb::g_mirror_host[dev] = 0;
     *out = w;
     return 0;
 }

@@ -323,3 +323,9 @@ extern "C" int lcb_fill_splitmix64(void *dst, size_t bytes, uint64_t seed, lcbSt
         static_cast<uint64_t *>(dst), nwords, seed, static_cast<uint8_t *>(dst) + nwords * 8, tail);
     return check_launch();
 }
+
+extern "C" int lcb_fill_splitmix64_at(void *dst, size_t bytes, uint64_t seed, uint64_t first_word, lcbStream stream) {
+    // word first_word + i of the stream is mix64(seed + (first_word + i + 1) * golden): the same stream started
+    // from a shifted seed
+    return lcb_fill_splitmix64(dst, bytes, seed + first_word * lcb::kGolden, stream);
+}

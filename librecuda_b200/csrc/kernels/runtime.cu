@@ -1,5 +1,6 @@
 // Process-wide state of the kernel layer: tunables, cached device properties, the sticky device error
 // word, and the small timing helpers the benchmark uses on raw CUDA streams.
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <string>
@@ -16,12 +17,12 @@ static const Tuning kDefaults = {
         /*copy_vec_unroll*/ 0,
         /*copy_vec_ctas_sm*/ 0,
         /*copy_cache_mode*/ 2,
-        /*tma_chunk*/ 32768,
+        /*tma_chunk*/ 0,
         /*tma_stages*/ 2,
         /*tma_lookahead*/ 1,
         /*tma_ctas_sm*/ 0,
         /*tma_cache_hint*/ 0,
-        /*auto_tma_min_mib*/ 2048,
+        /*auto_tma_min_mib*/ 96,
         /*memset_path*/ 0,
         /*memset_unroll*/ 8,
         /*memset_threads*/ 256,
@@ -44,27 +45,64 @@ static const Tuning kDefaults = {
         /*bcast_piece_mib*/ 64,
         /*bcast_pull_ctas*/ 74,
         /*bcast_engine_piece_mib*/ 0,
+        /*bcast_mc_piece_mib*/ 256,
+        /*bcast_mc_slots*/ 2,
+        /*bcast_mc_ctas*/ 64,
 };
+
+static void apply_env_overrides() {  // LCB_TUNE="knob=value,knob=value": overrides for experiments
+    const char *e = std::getenv("LCB_TUNE");
+    if (e == nullptr) return;
+    std::string all(e);
+    size_t pos = 0;
+    while (pos < all.size()) {
+        size_t end = all.find(',', pos);
+        if (end == std::string::npos) end = all.size();
+        const std::string item = all.substr(pos, end - pos);
+        const size_t eq = item.find('=');
+        if (eq != std::string::npos && lcb_tune(item.substr(0, eq).c_str(), std::atoi(item.c_str() + eq + 1)) != 0)
+            fprintf(stderr, "LCB_TUNE: '%s' refused (unknown knob or value out of range)\n", item.c_str());
+        pos = end + 1;
+    }
+}
 
 Tuning &tuning() {
     static Tuning t = kDefaults;
     static bool env_read = false;
-    if (!env_read) {  // LCB_TUNE="knob=value,knob=value": overrides for experiments, applied once
+    if (!env_read) {  // applied once at first use, and again after lcb_tune("reset", 0)
         env_read = true;
-        if (const char *e = std::getenv("LCB_TUNE")) {
-            std::string all(e);
-            size_t pos = 0;
-            while (pos < all.size()) {
-                size_t end = all.find(',', pos);
-                if (end == std::string::npos) end = all.size();
-                const std::string item = all.substr(pos, end - pos);
-                const size_t eq = item.find('=');
-                if (eq != std::string::npos) lcb_tune(item.substr(0, eq).c_str(), std::atoi(item.c_str() + eq + 1));
-                pos = end + 1;
-            }
-        }
+        apply_env_overrides();
     }
     return t;
+}
+
+// Accepted range of every knob.  A value outside it is refused and the previous value stays: a CTA of one
+// warp has nobody to copy the tail bytes, a thread count of 0 divides by zero, more than 512 threads breaks
+// the kernels' launch bounds, and ring shapes exist only as the instantiated (stages, lookahead) pairs.
+static bool knob_value_ok(const char *name, int v) {
+    auto is = [&](const char *n) { return std::strcmp(name, n) == 0; };
+    auto threads_ok = [&](int lo) { return v >= lo && v <= 512 && (v % 32) == 0; };
+    if (is("copy_vec_threads")) return v == 0 || threads_ok(64);
+    if (is("copy_vec_unroll")) return v == 0 || v == 1 || v == 2 || v == 4 || v == 8;
+    if (is("memset_threads")) return threads_ok(64);
+    if (is("memset_unroll")) return v == 1 || v == 2 || v == 4 || v == 8;
+    if (is("copy_cache_mode")) return v >= 0 && v <= 4;
+    if (is("tma_chunk") && v == 0) return true;  // 0: chunk, stages and lookahead chosen by size
+    if (is("tma_chunk") || is("tma2_chunk") || is("memset_chunk")) return v >= 1024 && v <= 65536 && (v & 127) == 0;
+    if (is("tma_stages")) return v >= 2 && v <= 16;
+    if (is("tma_lookahead")) return v >= 1 && v <= 12;
+    if (is("tma2_stages")) return v >= 4 && v <= 24;
+    if (is("tma2_depth")) return v >= 1 && v <= 8;
+    if (is("memset_path")) return v >= 0 && v <= 2;
+    if (is("memset_issuers")) return v >= 1 && v <= 8;
+    if (is("memset_bulk_ctas_sm")) return v >= 1 && v <= 32;
+    if (is("tma_cache_hint") || is("memset_cache_hint") || is("pdl")) return v == 0 || v == 1;
+    if (is("auto_tma_min_mib")) return v >= -1;
+    if (is("copy_vec_smem_pad") || is("tma_smem_pad") || is("memset_smem_pad")) return v >= 0 && v <= 200 * 1024;
+    if (is("bcast_pull_ctas")) return v >= 0 && v <= 65536;
+    if (is("bcast_mc_piece_mib")) return v >= 1 && v <= 1024;
+    if (is("bcast_mc_slots")) return v >= 2 && v <= 16;
+    return v >= 0;  // grid caps, thresholds and piece sizes: any non-negative value
 }
 
 int sm_count() {
@@ -83,50 +121,58 @@ int check_launch() { return (int)cudaGetLastError(); }
 
 }  // namespace lcb
 
+#define LCB_ALL_KNOBS(X) \
+    X(copy_vec_threads) \
+    X(copy_vec_unroll) \
+    X(copy_vec_ctas_sm) \
+    X(copy_cache_mode) \
+    X(tma_chunk) \
+    X(tma_stages) \
+    X(tma_lookahead) \
+    X(tma_ctas_sm) \
+    X(tma_cache_hint) \
+    X(auto_tma_min_mib) \
+    X(memset_path) \
+    X(memset_unroll) \
+    X(memset_threads) \
+    X(memset_ctas_sm) \
+    X(memset_chunk) \
+    X(memset_issuers) \
+    X(memset_bulk_ctas_sm) \
+    X(memset_cache_hint) \
+    X(pdl) \
+    X(copy_vec_smem_pad) \
+    X(tma_smem_pad) \
+    X(memset_smem_pad) \
+    X(fill_ctas_sm) \
+    X(axpb_ctas_sm) \
+    X(a2a_ctas_sm) \
+    X(tma2_depth) \
+    X(tma2_stages) \
+    X(tma2_chunk) \
+    X(peer_copy_engine) \
+    X(bcast_piece_mib) \
+    X(bcast_pull_ctas) \
+    X(bcast_engine_piece_mib) \
+    X(bcast_mc_piece_mib) \
+    X(bcast_mc_slots) \
+    X(bcast_mc_ctas)
+
 extern "C" int lcb_tune(const char *name, int value) {
     using lcb::tuning;
     if (name == nullptr) return 1;
-    if (std::strcmp(name, "reset") == 0) {  // back to the shipped configuration
+    if (std::strcmp(name, "reset") == 0) {  // back to the configuration the process started with
         tuning() = lcb::kDefaults;
+        lcb::apply_env_overrides();
         return 0;
     }
+    if (!lcb::knob_value_ok(name, value)) return 1;
 #define LCB_KNOB(field)                  \
     if (std::strcmp(name, #field) == 0) { \
         tuning().field = value;          \
         return 0;                        \
     }
-    LCB_KNOB(copy_vec_threads)
-    LCB_KNOB(copy_vec_unroll)
-    LCB_KNOB(copy_vec_ctas_sm)
-    LCB_KNOB(copy_cache_mode)
-    LCB_KNOB(tma_chunk)
-    LCB_KNOB(tma_stages)
-    LCB_KNOB(tma_lookahead)
-    LCB_KNOB(tma_ctas_sm)
-    LCB_KNOB(tma_cache_hint)
-    LCB_KNOB(auto_tma_min_mib)
-    LCB_KNOB(memset_path)
-    LCB_KNOB(memset_unroll)
-    LCB_KNOB(memset_threads)
-    LCB_KNOB(memset_ctas_sm)
-    LCB_KNOB(memset_chunk)
-    LCB_KNOB(memset_issuers)
-    LCB_KNOB(memset_bulk_ctas_sm)
-    LCB_KNOB(memset_cache_hint)
-    LCB_KNOB(pdl)
-    LCB_KNOB(copy_vec_smem_pad)
-    LCB_KNOB(tma_smem_pad)
-    LCB_KNOB(memset_smem_pad)
-    LCB_KNOB(fill_ctas_sm)
-    LCB_KNOB(axpb_ctas_sm)
-    LCB_KNOB(a2a_ctas_sm)
-    LCB_KNOB(tma2_depth)
-    LCB_KNOB(tma2_stages)
-    LCB_KNOB(tma2_chunk)
-    LCB_KNOB(peer_copy_engine)
-    LCB_KNOB(bcast_piece_mib)
-    LCB_KNOB(bcast_pull_ctas)
-    LCB_KNOB(bcast_engine_piece_mib)
+    LCB_ALL_KNOBS(LCB_KNOB)
 #undef LCB_KNOB
     return 1;
 }
@@ -136,13 +182,7 @@ extern "C" int lcb_tune_get(const char *name) {
     if (name == nullptr) return -1;
 #define LCB_KNOB(field) \
     if (std::strcmp(name, #field) == 0) return tuning().field;
-    LCB_KNOB(bcast_piece_mib)
-    LCB_KNOB(bcast_pull_ctas)
-    LCB_KNOB(bcast_engine_piece_mib)
-    LCB_KNOB(peer_copy_engine)
-    LCB_KNOB(a2a_ctas_sm)
-    LCB_KNOB(pdl)
-    LCB_KNOB(auto_tma_min_mib)
+    LCB_ALL_KNOBS(LCB_KNOB)
 #undef LCB_KNOB
     return -1;
 }
@@ -150,6 +190,7 @@ extern "C" int lcb_tune_get(const char *name) {
 extern "C" int lcb_preload(void) {
     int rc = lcb::preload_copy_kernels();
     if (rc == 0) rc = lcb::preload_fill_kernels();
+    if (rc == 0) rc = lcb::setup_error_mirror();
     return rc;
 }
 

@@ -39,6 +39,7 @@ class Launch(C.Structure):
 
 vp, sz, u64 = C.c_void_p, C.c_size_t, C.c_uint64
 lib.orc_fill_bytes.argtypes = [vp, sz, u64]
+lib.orc_fill_window.argtypes = [vp, sz, u64, u64]
 lib.orc_fill_f32.argtypes = [vp, sz, u64]
 lib.orc_ref_d2d_plan.argtypes = [u64, C.POINTER(Launch)]
 lib.orc_ref_d2d_run.argtypes = [vp, vp, u64]
@@ -60,6 +61,16 @@ lib.orc_mt_run.restype = C.c_double
 def random_bytes(n: int, seed: int) -> np.ndarray:
     a = np.empty(n, np.uint8)
     lib.orc_fill_bytes(a.ctypes.data, n, seed)
+    return a
+
+
+def random_window(byte_offset: int, n: int, seed: int) -> np.ndarray:
+    """Bytes [byte_offset, byte_offset + n) of the seeded stream that random_bytes(., seed) starts; the offset
+    must be a multiple of 8 (the generator is keyed by 64-bit word position)."""
+    if byte_offset % 8:
+        raise ValueError("window offset must be a multiple of 8")
+    a = np.empty(n, np.uint8)
+    lib.orc_fill_window(a.ctypes.data, n, seed, byte_offset // 8)
     return a
 
 

@@ -32,18 +32,23 @@ static inline uint64_t orc_mix64(uint64_t z) {
     return z ^ (z >> 31);
 }
 
-/* Seeded byte stream: 64-bit word i = mix64(seed + (i+1) * golden), little-endian. */
-void orc_fill_bytes(uint8_t *dst, size_t n, uint64_t seed) {
+/* Seeded byte stream: 64-bit word i = mix64(seed + (i+1) * golden), little-endian.  The stream is keyed by
+ * position, so any window of it can be produced without the bytes before it: orc_fill_window writes the n
+ * bytes that start at word `first_word` of the stream (a window deep inside a multi-GiB buffer costs only
+ * its own length). */
+void orc_fill_window(uint8_t *dst, size_t n, uint64_t seed, uint64_t first_word) {
     size_t nw = n / 8, i;
     for (i = 0; i < nw; ++i) {
-        uint64_t w = orc_mix64(seed + (uint64_t)(i + 1) * ORC_GOLDEN);
+        uint64_t w = orc_mix64(seed + (first_word + (uint64_t)i + 1) * ORC_GOLDEN);
         memcpy(dst + 8 * i, &w, 8);
     }
     if (n & 7) {
-        uint64_t w = orc_mix64(seed + (uint64_t)(nw + 1) * ORC_GOLDEN);
+        uint64_t w = orc_mix64(seed + (first_word + (uint64_t)nw + 1) * ORC_GOLDEN);
         memcpy(dst + 8 * nw, &w, n & 7);
     }
 }
+
+void orc_fill_bytes(uint8_t *dst, size_t n, uint64_t seed) { orc_fill_window(dst, n, seed, 0); }
 
 /* Uniform floats in [0,1): top 24 bits of word i scaled by 2^-24. */
 void orc_fill_f32(float *dst, size_t n, uint64_t seed) {

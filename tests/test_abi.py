@@ -130,4 +130,48 @@ def test_tunables_roundtrip_and_environment_override():
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=str(INCLUDE.parent),
                          env={**__import__("os").environ, "LCB_TUNE": "a2a_ctas_sm=7,pdl=0,bogus=3"})
     assert out.returncode == 0, out.stderr
-    assert out.stdout.split() == ["7", "0", "2048"]
+    assert out.stdout.split() == ["7", "0", "96"]
+
+
+def test_tunables_refuse_values_that_would_break_a_kernel():
+    # a refused value leaves the previous one in place; "reset" returns to the start-up configuration
+    lib = N.lib
+    assert lib.lcb_tune(b"memset_threads", 128) == 0
+    for knob, bad in ((b"memset_threads", 32), (b"memset_threads", 0), (b"memset_threads", 1024), (b"memset_threads", 100),
+                      (b"copy_vec_threads", 32), (b"copy_vec_threads", -64), (b"copy_vec_threads", 544),
+                      (b"copy_vec_unroll", 3), (b"memset_unroll", 0), (b"copy_cache_mode", 9), (b"tma_chunk", 1000),
+                      (b"tma_chunk", 131072), (b"tma_stages", 1), (b"tma_lookahead", 0), (b"pdl", 2), (b"a2a_ctas_sm", -1)):
+        before = lib.lcb_tune_get(knob)
+        assert lib.lcb_tune(knob, bad) == 1, (knob, bad)
+        assert lib.lcb_tune_get(knob) == before, (knob, bad)
+    assert lib.lcb_tune_get(b"memset_threads") == 128
+    assert lib.lcb_tune(b"copy_vec_threads", 0) == 0 and lib.lcb_tune(b"copy_vec_threads", 256) == 0
+    assert lib.lcb_tune(b"reset", 0) == 0
+    assert lib.lcb_tune_get(b"memset_threads") == 256 and lib.lcb_tune_get(b"copy_vec_threads") == 0
+
+
+def test_copy_plan_query_follows_the_dispatcher():
+    # no GPU needed: the query runs the dispatcher's own decision code without launching
+    lib = N.lib
+    buf = C.create_string_buffer(200)
+
+    def plan(dst, src, n, path=0):
+        assert lib.lcb_copy_d2d_describe(dst, src, n, path, 0, buf, 200) == 0
+        return buf.value.decode()
+
+    MiB = 1 << 20
+    assert plan(4096, 1 << 40, 4096).startswith("copy_vec_kernel<-1,1,")              # small path
+    assert plan(4096, 1 << 40, 32 * MiB).startswith("copy_vec_kernel<-1,")           # vector kernel below 96 MiB
+    assert plan(4096, 1 << 40, 256 * MiB).startswith("copy_tma_kernel<3,2,0>, 32768 CTAs")   # 8 KiB chunks
+    assert plan(4096, 1 << 40, 1 << 30).startswith("copy_tma_kernel<2,1,0>, 32768 CTAs")     # 32 KiB chunks
+    assert plan(4096, (1 << 40) + 1, 1 << 30).startswith("copy_vec_kernel<0,4,2>, 32768 CTAs x 512")  # realign by 1 byte
+    assert plan(4096, (1 << 40) + 13, 1 << 30).startswith("copy_vec_kernel<3,4,2>")
+    assert "loads before the stream wait" in plan(4096, 1 << 40, 1 << 30, 0x100)
+    assert "loads before the stream wait" not in plan(4096, 1 << 40, 1 << 30, 0)
+    assert lib.lcb_copy_d2d_describe(4096, (1 << 40) + 1, 1 << 20, 2, 0, buf, 200) == 1      # bulk path refused
+    assert lib.lcb_copy_d2d_describe(4096, 1 << 40, 1 << 20, 0x400, 0, buf, 200) == 1        # unknown flag
+    lib.lcb_tune(b"auto_tma_min_mib", -1)
+    try:
+        assert plan(4096, 1 << 40, 1 << 30).startswith("copy_vec_kernel<-1,2,2>, 262144 CTAs x 128")
+    finally:
+        lib.lcb_tune(b"reset", 0)

@@ -10,11 +10,13 @@ import pytest
 
 import oracle
 from librecuda_b200 import api
-from gpu_util import GUARD, GUARD_BYTE, device_checksum, device_compare, to_device, to_host
+from gpu_util import (GUARD, GUARD_BYTE, device_checksum, device_compare, host_window_mismatches, seeded_stream_expect,
+                      to_device, to_host)
 
 pytestmark = pytest.mark.gpu
 MiB = 1 << 20
 AUTO, VEC, TMA, SMALL, VEC32, TMA2 = 0, 1, 2, 3, 4, 5
+SRC_STABLE, NO_PDL = 0x100, 0x200   # flags OR'ed into the path argument
 GOLDEN = json.loads((Path(__file__).parent / "golden" / "ref_d2d_golden.json").read_text())
 
 
@@ -85,6 +87,38 @@ def test_mid_and_large_sizes(stream, path):
     sizes = [MiB - 1, MiB, MiB + 131, 2 * MiB + 5, 3 * MiB + 4099, 16 * MiB + 4100, 64 * MiB + 17]
     offs = [(0, 0), (64, 64), (16, 48)] if path in (TMA, TMA2) else [(0, 0), (1, 0), (0, 3), (7, 7), (64, 1), (3, 64), (5, 9)]
     _run_cases(stream, [(n, so, do) for n in sizes for so, do in offs], path)
+
+
+@pytest.mark.parametrize("path", [AUTO | SRC_STABLE, VEC | SRC_STABLE, SMALL | SRC_STABLE, AUTO | NO_PDL, AUTO | SRC_STABLE | NO_PDL])
+def test_launch_flags_do_not_change_the_result(stream, path):
+    # SRC_STABLE lets the loads run ahead of the wait for the previous kernel on the stream; the copies of one
+    # arena are launched back to back, so every launch overlaps the tail of the one before it
+    sizes = [1, 15, 16, 17, 4097, 65535, 65536, MiB + 131, 3 * MiB + 4099, 16 * MiB + 4100]
+    offs = [(0, 0), (1, 0), (0, 3), (7, 7), (64, 1), (5, 9)]
+    _run_cases(stream, [(n, so, do) for n in sizes for so, do in offs], path)
+
+
+def test_loads_ahead_of_the_wait_on_the_bulk_path(stream):
+    cases = [(n, o, o + 16 * k) for n in (1, 17, 16385, 3 * 16384 + 7, 200001, 7 * MiB + 33, 130 * MiB + 5)
+             for o in (0, 5) for k in (0, 2)]
+    _run_cases(stream, cases, TMA | SRC_STABLE)
+    api.tune(tma_ctas_sm=1, tma_chunk=8192, tma_stages=8, tma_lookahead=6)   # persistent ring
+    try:
+        _run_cases(stream, cases, TMA | SRC_STABLE)
+    finally:
+        api.tune_reset()
+
+
+def test_copy_plan_query_names_what_is_launched(stream):
+    import ctypes as C
+    buf = C.create_string_buffer(200)
+    a, b = api.DeviceBuffer(300 * MiB), api.DeviceBuffer(300 * MiB)
+    for n, off, want in ((4096, 0, "copy_vec_kernel<-1,1,2>"), (200 * MiB, 0, "copy_tma_kernel<3,2,0>"),
+                         (200 * MiB, 3, "copy_vec_kernel<0,4,2>"), (64 * MiB, 0, "copy_vec_kernel<-1,4,2>")):
+        assert api.lib.lcb_copy_d2d_describe(b.ptr, a.ptr + off, n, AUTO, 0, buf, 200) == 0
+        assert buf.value.decode().startswith(want), buf.value
+    a.free()
+    b.free()
 
 
 @pytest.mark.parametrize("path", [TMA, TMA2])
@@ -220,9 +254,12 @@ def test_device_helpers_agree_with_oracle(stream):
 SWEEP_OFFSETS = [0, 1, 3, 7, 64]
 
 
-def _sweep(stream, sizes, pairs):
+def _sweep(stream, sizes, pairs, host_pairs=()):
     """DtoD sweep with everything verified on the device: seeded source (seed 1), compare against the
-    source range, guard bands either side of the destination, and checksum(src) == checksum(dst)."""
+    source range, guard bands either side of the destination, and checksum(src) == checksum(dst).  For the
+    offset pairs in `host_pairs` the destination is ALSO checked on the host: windows of it (first, last, three
+    random ones and, past 4 GiB, one that straddles the 4 GiB offset) are copied back and compared with the
+    oracle's own regeneration of the seeded stream, so no kernel of this library judges that part."""
     top = max(sizes)
     src = api.DeviceBuffer(top + 128)
     dst = api.DeviceBuffer(top + 128 + 2 * GUARD)
@@ -232,6 +269,8 @@ def _sweep(stream, sizes, pairs):
     stream.memset_d8(guard, GUARD_BYTE, GUARD)
     stream.run()
     api.lcb_check(api.lib.lcb_fill_splitmix64(src.ptr, top + 128, 1, stream.native), "fill")
+    # the generator itself, against the host oracle, over the whole source (windows incl. the 4 GiB boundary)
+    assert host_window_mismatches(stream, src.ptr, top + 128, seeded_stream_expect(1), salt=1, extra_offsets=STRADDLE) == []
     for n in sizes:
         for so, do in pairs:
             d = dst.ptr + GUARD + do
@@ -241,6 +280,10 @@ def _sweep(stream, sizes, pairs):
             assert device_compare(stream, d, src.ptr + so, n, res)[0] == 0, (n, so, do)
             assert device_compare(stream, d - GUARD, guard.ptr, GUARD, res)[0] == 0, ("front guard", n, so, do)
             assert device_compare(stream, d + n, guard.ptr, GUARD, res)[0] == 0, ("back guard", n, so, do)
+            if (so, do) in host_pairs and n >= (1 << 20):
+                bad = host_window_mismatches(stream, d, n, seeded_stream_expect(1, so), salt=n % 977 + so,
+                                             extra_offsets=[o - so for o in STRADDLE])
+                assert bad == [], (n, so, do, bad)
         # 8-byte aligned pair for the checksum property
         api.lcb_check(api.lib.lcb_copy_d2d(dst.ptr + GUARD, src.ptr + 64, n, stream.native), "lcb_copy_d2d")
         assert device_checksum(stream, dst.ptr + GUARD, n, scratch, out) == device_checksum(stream, src.ptr + 64, n, scratch, out)
@@ -249,11 +292,47 @@ def _sweep(stream, sizes, pairs):
         b.free()
 
 
+# windows that start 8 MiB before a 4 GiB multiple of the source stream: 32-bit index slips show up there
+STRADDLE = [(4 << 30) - (8 << 20), (8 << 30) - (16 << 20)]
+
+
 def test_dtod_sweep_powers_of_two_all_offset_pairs(stream):
     # 4 KiB ... 1 GiB, src/dst offsets {0,1,3,7,64}^2
-    _sweep(stream, [1 << k for k in range(12, 31)], [(a, b) for a in SWEEP_OFFSETS for b in SWEEP_OFFSETS])
+    _sweep(stream, [1 << k for k in range(12, 31)], [(a, b) for a in SWEEP_OFFSETS for b in SWEEP_OFFSETS],
+           host_pairs=[(0, 0), (1, 3), (64, 7)])
 
 
 def test_dtod_sweep_largest_sizes(stream):
     # 2, 4 and 8 GiB: 64-bit offsets everywhere (the reference over-launches from 256 MiB on)
-    _sweep(stream, [1 << 31, 1 << 32, 1 << 33], [(a, b) for a in SWEEP_OFFSETS for b in SWEEP_OFFSETS])
+    pairs = [(a, b) for a in SWEEP_OFFSETS for b in SWEEP_OFFSETS]
+    _sweep(stream, [1 << 31, 1 << 32, 1 << 33], pairs, host_pairs=pairs)
+
+
+def test_host_window_check_catches_one_wrong_byte_past_4_gib(stream):
+    # the negative of the check above: an 8 GiB copy is right, but the HOST side of the comparison is given one
+    # flipped byte at stream position 4 GiB + 12345; the window that straddles 4 GiB must report it, and only it
+    n = 1 << 33
+    src, dst = api.DeviceBuffer(n), api.DeviceBuffer(n)
+    api.lcb_check(api.lib.lcb_fill_splitmix64(src.ptr, n, 1, stream.native), "fill")
+    api.lcb_check(api.lib.lcb_copy_d2d(dst.ptr, src.ptr, n, stream.native), "lcb_copy_d2d")
+    truth = seeded_stream_expect(1)
+    planted_at = (4 << 30) + 12345
+
+    def planted(off, m):
+        w = truth(off, m).copy()
+        if off <= planted_at < off + m:
+            w[planted_at - off] ^= 0x01
+        return w
+
+    assert host_window_mismatches(stream, dst.ptr, n, truth, salt=3, extra_offsets=STRADDLE) == []
+    assert host_window_mismatches(stream, dst.ptr, n, planted, salt=3, extra_offsets=STRADDLE) == [STRADDLE[0]]
+    # and a wrong byte on the DEVICE side at the same place is caught the same way
+    flip = np.array([0], np.uint8)
+    stream.memcpy(flip, dst.ptr + planted_at, 1)
+    stream.run()
+    flip ^= 0x80
+    stream.memcpy(dst.ptr + planted_at, flip, 1)
+    stream.run()
+    assert host_window_mismatches(stream, dst.ptr, n, truth, salt=3, extra_offsets=STRADDLE) == [STRADDLE[0]]
+    src.free()
+    dst.free()

@@ -306,6 +306,141 @@ def test_events_timing_and_states(stream, module):
     out.free()
 
 
+def test_await_reports_a_kernel_that_gave_up_a_bounded_wait(stream):
+    # a copy whose bulk ring gives up a wait is incomplete although the stream finishes without a CUDA error; a
+    # program written for the reference only looks at the status of Await, so Await has to say so.  The give-up
+    # path is driven by the self-test kernel (a wait nothing completes, small try limit): no fault, no hang.
+    stream.run()
+    assert api.device_error_word() == 0
+    api.lcb_check(lib.lcb_selftest_wait_timeout(2000, stream.native), "selftest")
+    assert lib.libreCuStreamAwait(stream.handle) == api.ERROR_UNKNOWN      # reported once ...
+    assert lib.libreCuStreamAwait(stream.handle) == api.SUCCESS            # ... and cleared
+    assert api.device_error_word() == 0
+    # the same through an event
+    ev = api.Event()
+    api.lcb_check(lib.lcb_selftest_wait_timeout(2000, stream.native), "selftest")
+    ev.record(stream)
+    stream.commence()
+    assert lib.libreCuEventSynchronize(ev.handle) == api.ERROR_UNKNOWN
+    assert lib.libreCuEventSynchronize(ev.handle) == api.SUCCESS
+    stream.run()
+    ev.destroy()
+    # and the stream still copies
+    src = np.arange(100000, dtype=np.uint8)
+    d, out = api.DeviceBuffer(100000), np.zeros(100000, np.uint8)
+    stream.memcpy(d, src, 100000)
+    stream.memcpy(out, d, 100000)
+    stream.run()
+    assert np.array_equal(out, src)
+    d.free()
+
+
+def test_host_wait_deadline_from_the_environment():
+    # LIBRECUDA_WAIT_TIMEOUT_MS is read once per process, so the case runs in a child: a kernel that spins for
+    # 0.4 s (bounded by its cycle count, nothing hangs), a 50 ms limit -> Await and EventSynchronize give up with
+    # NOT_READY while it runs, and succeed when repeated after it has finished
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    code = """
+import ctypes as C, sys, time
+from librecuda_b200 import api
+from pathlib import Path
+lib = api.lib
+ctx = api.Context(0)
+m = api.Module(Path(sys.argv[1]).read_bytes())
+fn = m.function("spin_then_increment")
+st = api.Stream()
+out = api.DeviceBuffer(4, map_to_cpu=True)
+C.c_float.from_address(out.ptr).value = 0.0
+ev = api.Event()
+st.launch(fn, (1, 1, 1), (1, 1, 1), 0, [C.c_void_p(out.ptr), C.c_longlong(int(0.4 * 1.9e9))])
+ev.record(st)
+st.commence()
+t0 = time.perf_counter()
+a = lib.libreCuStreamAwait(st.handle)
+t1 = time.perf_counter()
+b = lib.libreCuEventSynchronize(ev.handle)
+t2 = time.perf_counter()
+time.sleep(0.6)
+c = lib.libreCuStreamAwait(st.handle)
+d = lib.libreCuEventSynchronize(ev.handle)
+print(a, b, c, d, round(t1 - t0, 3), round(t2 - t1, 3), C.c_float.from_address(out.ptr).value)
+"""
+    root = Path(__file__).resolve().parent.parent
+    run = subprocess.run([sys.executable, "-c", code, str(FIXTURE_CUBIN)], capture_output=True, text=True, timeout=120, cwd=str(root),
+                         env={**os.environ, "LIBRECUDA_WAIT_TIMEOUT_MS": "50"})
+    assert run.returncode == 0, run.stderr[-2000:]
+    a, b, c, d, dt_await, dt_event, value = run.stdout.split()
+    assert (int(a), int(b)) == (api.ERROR_NOT_READY, api.ERROR_NOT_READY)
+    assert (int(c), int(d)) == (api.SUCCESS, api.SUCCESS)
+    assert 0.04 < float(dt_await) < 0.3 and 0.04 < float(dt_event) < 0.3
+    assert float(value) == 1.0
+
+
+def test_event_timestamps_keep_their_resolution_across_epochs(stream):
+    # timestamps are measured against a chain of epochs (a new one every couple of seconds of activity), not as
+    # one float distance from context creation: two events microseconds apart must not collapse, and the
+    # distance between events seconds apart must agree with the host clock
+    import time
+    a, b, c, d = (api.Event() for _ in range(4))
+    a.record(stream)
+    stream.run()
+    t0 = time.perf_counter()
+    time.sleep(2.3)                       # long enough for the next record to start a new epoch
+    b.record(stream)
+    buf = api.DeviceBuffer(64 << 20)
+    stream.memset_d8(buf, 1, 64 << 20)    # ~10 us of work between b and c
+    c.record(stream)
+    stream.run()
+    host_ns = (time.perf_counter() - t0) * 1e9
+    time.sleep(2.3)
+    d.record(stream)
+    stream.run()
+    ta, tb, tc, td = (e.timestamp_ns() for e in (a, b, c, d))
+    assert ta < tb < tc < td
+    assert 2.0e9 < tb - ta < host_ns + 0.2e9
+    assert 2_000 < tc - tb < 2_000_000    # microseconds, not zero and not the float step of an old origin
+    assert abs((tc - tb) - api.elapsed_ms(b, c) * 1e6) < 2_000
+    assert td - tc > 2.0e9
+    for e in (a, b, c, d):
+        e.destroy()
+    buf.free()
+
+
+def test_copy_chain_with_loads_ahead_of_the_wait_stays_ordered(stream):
+    # the stream layer lets a copy load before the previous kernel has drained only when nothing in flight writes
+    # its source; a chain a -> b -> c -> d (every source written by the kernel before it), interleaved with
+    # independent copies and memsets, must still give exactly the sequential result
+    n = 24 << 20
+    rng = np.random.default_rng(5)
+    host = rng.integers(0, 256, n, dtype=np.uint8)
+    bufs = [api.DeviceBuffer(n + 64) for _ in range(5)]
+    stream.memcpy(bufs[0], host, n)
+    stream.run()
+    for rep in range(3):
+        stream.memset_d8(bufs[4], rep, n)                      # independent of the chain
+        stream.memcpy(bufs[1].view(1, n), bufs[0], n)          # a -> b (misaligned destination)
+        stream.memcpy(bufs[2], bufs[1].view(1, n), n)          # b -> c: source written by the copy before
+        stream.memset_d8(bufs[3], 0xEE, n)
+        stream.memcpy(bufs[3].view(16, n // 2), bufs[2], n // 2)   # c -> d (first half)
+        stream.memcpy(bufs[0], bufs[2], n)                     # c -> a: same bytes back
+        stream.memcpy(bufs[4], bufs[3], n)                     # d -> e: half 0xEE, half data shifted by 16
+    out = np.zeros(n, np.uint8)
+    stream.memcpy(out, bufs[4], n)
+    stream.run()
+    want = np.full(n, 0xEE, np.uint8)
+    want[16:16 + n // 2] = host[:n // 2]
+    assert np.array_equal(out, want)
+    stream.memcpy(out, bufs[0], n)
+    stream.run()
+    assert np.array_equal(out, host)
+    for b in bufs:
+        b.free()
+
+
 def test_stream_wait_event_orders_across_streams(ctx, module):
     fn = module.function("spin_then_increment")
     a, b = api.Stream(), api.Stream()

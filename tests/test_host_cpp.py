@@ -1,5 +1,6 @@
 """Sanitizer builds of the host-only C++ pieces (no CUDA needed): the worker pool behind the pageable-copy
-staging ring under AddressSanitizer+UBSan and under ThreadSanitizer."""
+staging ring under AddressSanitizer+UBSan and under ThreadSanitizer, and the stream layer's decision logic
+(wait with a deadline against a query that never succeeds, timestamp accumulation, the in-flight write log)."""
 import subprocess
 from pathlib import Path
 
@@ -21,3 +22,15 @@ def test_copy_pool_under_sanitizers(tmp_path, san):
         pytest.skip("ThreadSanitizer cannot run under this kernel's address-space layout")
     assert run.returncode == 0, (run.stdout + run.stderr)[-3000:]
     assert "copy pool ok" in run.stdout
+
+
+def test_stream_layer_host_logic(tmp_path):
+    src = ROOT / "tests" / "cpp" / "host_logic_test.cpp"
+    exe = tmp_path / "host_logic_test"
+    build = subprocess.run(["g++", "-std=c++17", "-O1", "-g", "-Wall", "-Wextra", "-Werror", "-fsanitize=address,undefined",
+                            "-fno-omit-frame-pointer", f"-I{INC}", str(src), "-o", str(exe), "-pthread"],
+                           capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr[-2000:]
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert run.returncode == 0, (run.stdout + run.stderr)[-3000:]
+    assert "host logic ok" in run.stdout

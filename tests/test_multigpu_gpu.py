@@ -18,7 +18,7 @@ lib = api.lib
 def gpus(ctx, gpu_count):
     if gpu_count < 2:
         pytest.skip("needs >= 2 GPUs")
-    n = min(gpu_count, 4)
+    n = min(gpu_count, 8)
     ctxs = [ctx] + [api.Context(i) for i in range(1, n)]
     for c in ctxs:
         c.set_current()
@@ -229,13 +229,14 @@ def test_all_to_all_recorded_per_rank(gpus, pull):
     ctxs[0].set_current()
 
 
-@pytest.mark.parametrize("use_nccl", [0, 1, 2])
+@pytest.mark.parametrize("use_nccl", [0, 1, 2, 3])
 @pytest.mark.parametrize("root", [0, 1])
 def test_broadcast(gpus, use_nccl, root):
     ctxs, streams = gpus
     G = len(ctxs)
     n = 37 * MiB + 1001
     api.tune(bcast_engine_piece_mib=4)     # form 2 with more than two GPUs: ten pieces, the last one ragged
+    api.tune(bcast_mc_piece_mib=4, bcast_mc_slots=3)   # form 3: ten pieces through a ring of three slots, ragged end
     try:
         _broadcast(ctxs, streams, G, n, use_nccl, root)
     finally:
@@ -255,6 +256,41 @@ def _broadcast(ctxs, streams, G, n, use_nccl, root):
         s.await_()
     for g in range(G):
         assert np.array_equal(_download(ctxs, streams, g, bufs[g], n), data), f"rank {g}"
+    for g in range(G):
+        ctxs[g].set_current()
+        bufs[g].free()
+    ctxs[0].set_current()
+
+
+def test_multicast_broadcast_large_misaligned_destinations_and_repeats(gpus):
+    # form 3 (multimem stores through NVSwitch): default piece size, destinations at odd offsets (the local copy
+    # out of the staging slab realigns), the last root, twice in a row through the same ring of slots; a root
+    # buffer that is not 16-byte aligned takes the documented fall-back and must still deliver
+    ctxs, streams = gpus
+    G = len(ctxs)
+    n = 200 * MiB + 7
+    data = oracle.random_bytes(n, seed=33)
+    root = G - 1
+    bufs = [_alloc_on(ctxs[g], n + 64) for g in range(G)]
+    offs = [0 if g == root else (1 + 3 * g) % 16 for g in range(G)]
+    for rep, shift in ((0, 0), (1, 0), (2, 8)):
+        roff = shift if shift else 0
+        for g in range(G):
+            _upload(ctxs, streams, g, bufs[g], np.zeros(n + 64, np.uint8))
+        ctxs[root].set_current()
+        streams[root].memcpy(bufs[root].ptr + roff, data, n)
+        streams[root].run()
+        ctxs[0].set_current()
+        bp = (C.c_void_p * G)(*[b.ptr + (roff if g == root else offs[g]) for g, b in enumerate(bufs)])
+        stp = (C.c_void_p * G)(*[s.handle for s in streams])
+        api.check(lib.libreCuBroadcast(bp, root, n, G, stp, 3))
+        for s in streams:
+            s.await_()
+        for g in range(G):
+            got = _download(ctxs, streams, g, bufs[g], n + 64)
+            o = roff if g == root else offs[g]
+            assert np.array_equal(got[o:o + n], data), f"rep {rep} rank {g}"
+            assert not got[:o].any() and not got[o + n:].any(), f"rep {rep} rank {g}: bytes outside the range"
     for g in range(G):
         ctxs[g].set_current()
         bufs[g].free()

@@ -178,3 +178,24 @@ def test_mt_baseline_runs_and_copies():
     assert t > 0 and np.array_equal(dst, src)
     t = oracle.mt_seconds(dst, None, op=1, value=0x5A, threads=4, reps=1)
     assert t > 0 and (dst == 0x5A).all()
+
+
+def test_seeded_stream_windows_match_the_stream_and_a_pure_python_restatement():
+    # any window of the position-keyed stream equals the same bytes of the stream generated from its start ...
+    full = oracle.random_bytes(1 << 20, seed=7)
+    for off, n in ((0, 100), (8, 8), (4096 * 8, 1003), ((1 << 20) - 64, 64)):
+        assert np.array_equal(oracle.random_window(off, n, 7), full[off:off + n])
+    with pytest.raises(ValueError):
+        oracle.random_window(3, 8, 7)
+    # ... and far past 4 GiB it still follows the definition: word i = mix64(seed + (i + 1) * golden) mod 2^64
+    M, G = (1 << 64) - 1, 0x9E3779B97F4A7C15
+
+    def mix64(z):
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M
+        return z ^ (z >> 31)
+
+    for byte_off in ((4 << 30) - 8, 4 << 30, (7 << 30) + 4096):
+        w = oracle.random_window(byte_off, 24, 1).view("<u8")
+        i0 = byte_off // 8
+        assert [int(x) for x in w] == [mix64((1 + (i0 + k + 1) * G) & M) for k in range(3)]
