@@ -775,14 +775,37 @@ def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_r
             ok = ok and device_equal(api, stream, ptr + r * chunk, scratch.ptr, chunk, resb)
         return ok and host_windows_ok(api, stream, ptr, G * chunk, alltoall_expect(G, chunk, rank), salt=31 + rank)
 
+    # the copy-engine form: G-1 peer copies per rank kept in lock-step through flags in each other's memory (every
+    # GPU has one sender at a time), the local chunk as a kernel on a second stream beside them
+    flags = api.DeviceBuffer(4096)
+    stream.memset_d8(flags, 0, 4096)
+    stream.run()
+    flag_peers = mr.open_peers(dist, flags)
+    flag_arr = (C.c_void_p * G)(*flag_peers)
+    side = api.Stream()
+    epoch = [0]
+
+    def a2a_engines():
+        epoch[0] += 1
+        api.lcb_check(lib.lcb_stream_wait_stream(side.native, native), "fork")
+        api.lcb_check(lib.lcb_alltoall_engines(peer_arr, send.ptr, chunk, G, rank, flags.ptr, flag_arr, epoch[0], 2000,
+                                               native, side.native), "a2a engines")
+        api.lcb_check(lib.lcb_stream_wait_stream(native, side.native), "join")
+
     forms = (
         ("alltoall_own_push", lambda: api.lcb_check(lib.lcb_alltoall_push(peer_arr, send.ptr, chunk, G, rank, native), "a2a push")),
+        ("alltoall_copy_engines_lockstep", a2a_engines),
         ("alltoall_own_pull", lambda: api.lcb_check(lib.lcb_alltoall_pull(send_arr, recv.ptr, chunk, G, rank, native), "a2a pull")),
     )
     for name, fn in forms:
         clear_recv()
         measure(name, fn, (G - 1) * chunk)
-        out[name]["verified"] = verify_recv(recv.ptr)
+        out[name]["verified"] = verify_recv(recv.ptr) and api.device_error_word() == 0
+    side.destroy()
+    barrier()
+    mr.close_peers(dist, flag_peers)
+    barrier()
+    flags.free()
 
     # 3. partitioned copy of an 8 GiB buffer that lives on rank 0: shard g (2 MiB-aligned boundaries from
     #    libreCuPartitionPlan) is pulled by rank g into its own memory; rank 0 keeps shard 0 with a local copy.

@@ -27,7 +27,8 @@ enum lcbCopyPath {
     LCB_COPY_TMA = 2,   /* cp.async.bulk global->smem->global; needs (src-dst) % 16 == 0            */
     LCB_COPY_SMALL = 3, /* single small CTA wave, latency path                                     */
     LCB_COPY_VEC32 = 4, /* 32-byte vector loads+stores; needs (src-dst) % 32 == 0                   */
-    LCB_COPY_TMA2 = 5   /* bulk ring with separate load- and store-issuing threads; (src-dst) % 16 == 0 */
+    LCB_COPY_TMA2 = 5,  /* bulk ring with separate load- and store-issuing threads; (src-dst) % 16 == 0 */
+    LCB_COPY_PHASED = 6 /* bulk copies with all SMs loading and storing in alternating time slices; (src-dst) % 16 == 0 */
 };
 /* Flag that may be OR'ed into the `path` argument of lcb_copy_d2d_ex (LCB_COPY_AUTO, _VEC, _SMALL, _TMA):
  * the caller vouches that no work submitted earlier to `stream` and possibly still running writes the
@@ -92,6 +93,30 @@ int lcb_alltoall_push(void *const *peer_recv, const void *send, size_t chunk_byt
 int lcb_alltoall_pull(void *const *peer_send, void *recv, size_t chunk_bytes, int n_ranks, int rank,
                       lcbStream stream);
 
+/* One rank's half of an all-to-all on the COPY ENGINES, for ranks that live in different processes (one per
+ * GPU): n_ranks - 1 peer copies of chunk_bytes, rank r sending chunk (r + s) mod n to rank (r + s) mod n at step
+ * s, plus the local chunk by the copy kernel (on local_stream if it is not NULL, so that it runs beside the
+ * engine copies).  Engine copies only reach their rate (about 775 GB/s per direction against 707 for SM-issued
+ * stores) when every GPU has exactly ONE sender at a time, so the ranks keep in lock-step through flags in
+ * each other's memory: after a copy the sender posts `epoch` into a flag word of the rank that needs that
+ * receiver next, and that rank's copy waits for it with a one-thread kernel.  The wait is bounded by timeout_ms
+ * (1..10000); when it runs out the kernel raises bit 1 of the sticky error word (lcb_device_error_word) and
+ * the copies go on unsynchronised.
+ *   peer_recv[j]   rank j's receive buffer (n_ranks * chunk_bytes), mapped into this process;
+ *   flags          this rank's flag words: n_ranks unsigned ints, zero before the first call;
+ *   peer_flags[j]  rank j's flag words mapped into this process (HOST array of n_ranks device pointers);
+ *   epoch          1, 2, 3 ... : the same value on every rank for the same call, increased by one per call.
+ * With n_ranks <= 2 no flags are needed (they may be NULL).  ref: none (single-GPU reference, librecuda.cpp:61). */
+int lcb_alltoall_engines(void *const *peer_recv, const void *send, size_t chunk_bytes, int n_ranks, int rank,
+                         void *flags, void *const *peer_flags, unsigned int epoch, unsigned int timeout_ms,
+                         lcbStream stream, lcbStream local_stream);
+/* The two flag primitives it is built from.  lcb_flag_post: once everything earlier on `stream` has finished,
+ * store `value` to the 4-byte aligned word `flag` (any memory this GPU may write, a peer's included).
+ * lcb_flag_wait: work later on `stream` starts when the word has reached `value` (counters only grow), or
+ * after timeout_ms (1..10000) with bit 1 of the sticky error word raised. */
+int lcb_flag_post(void *flag, unsigned int value, lcbStream stream);
+int lcb_flag_wait(const void *flag, unsigned int value, unsigned int timeout_ms, lcbStream stream);
+
 /* Copies `bytes` bytes (a multiple of 16; both addresses 16-byte aligned) from ordinary device memory to a
  * MULTICAST address with multimem stores: NVSwitch writes the data into the memory of every GPU bound to the
  * multicast object at that offset, while it leaves the storing GPU only once.  mc_dst must be an address of a
@@ -136,8 +161,8 @@ size_t lcb_checksum_scratch_bytes(void);
 int lcb_checksum64_noalloc(const void *src, size_t bytes, uint64_t *out, lcbStream stream);
 size_t lcb_checksum64_noalloc_max_bytes(void);
 
-/* Reads and clears the per-device sticky word that kernels set when a bounded wait (mbarrier) gave
- * up: 0 = no error.  Synchronises the device. */
+/* Reads and clears the per-device sticky word that kernels set when a bounded wait gave up: bit 0 an mbarrier
+ * wait of the bulk-copy ring, bit 1 a wait for another GPU's flag; 0 = no error.  Synchronises the device. */
 int lcb_device_error_word(unsigned int *out);
 /* The same word as last mirrored into host memory by the kernels, read WITHOUT synchronising or clearing:
  * what a host that has just finished a stream wait consults (libreCuStreamAwait and libreCuEventSynchronize

@@ -36,6 +36,9 @@ LCB_FUNCTIONS = {
     "lcb_alltoall_push": (i32, [vpp, vp, sz, i32, i32, vp]),
     "lcb_alltoall_pull": (i32, [vpp, vp, sz, i32, i32, vp]),
     "lcb_multicast_store": (i32, [vp, vp, sz, i32, vp]),
+    "lcb_alltoall_engines": (i32, [vpp, vp, sz, i32, i32, vp, vpp, C.c_uint, C.c_uint, vp, vp]),
+    "lcb_flag_post": (i32, [vp, C.c_uint, vp]),
+    "lcb_flag_wait": (i32, [vp, C.c_uint, C.c_uint, vp]),
     "lcb_fill_splitmix64": (i32, [vp, sz, u64, vp]),
     "lcb_fill_splitmix64_at": (i32, [vp, sz, u64, u64, vp]),
     "lcb_compare_bytes": (i32, [vp, vp, sz, vp, vp]),

@@ -10,6 +10,8 @@ namespace lcb {
 // Bit 0 of the sticky per-device error word (defined beside the bulk-copy ring that sets it):
 // an mbarrier wait gave up.
 constexpr unsigned int kErrMbarrierTimeout = 1u;
+// Bit 1: a wait for a flag that another GPU posts gave up.
+constexpr unsigned int kErrFlagTimeout = 2u;
 
 // Tunables reachable through lcb_tune() (for sweeps; the defaults are the shipped configuration).
 struct Tuning {
@@ -46,6 +48,9 @@ struct Tuning {
     int bcast_piece_mib;     // own broadcast: MiB per pipelined piece
     int bcast_pull_ctas;     // own broadcast: CTAs of the kernel that pulls from the root (it must not fill the GPU)
     int bcast_engine_piece_mib;  // copy-engine chain broadcast: MiB per piece, 0 = chosen from the size and the number of GPUs
+    int phase_chunk;             // phase-grouped copy: bytes per bulk copy
+    int phase_stages;            // phase-grouped copy: bulk copies per CTA and phase (2, 3, 4, 6, 12 or 24)
+    int phase_ns;                // phase-grouped copy: length of a load / store time slice in ns (0: no slicing)
     int bcast_mc_piece_mib;      // multicast broadcast: MiB per piece
     int bcast_mc_slots;          // multicast broadcast: pieces in the staging ring of every GPU
     int bcast_mc_ctas;           // multicast broadcast: looping CTAs of the root's store kernel (0: one short CTA per tile)

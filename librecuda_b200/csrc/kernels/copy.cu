@@ -403,6 +403,83 @@ __global__ void __launch_bounds__(64) copy_tma2_kernel(uint8_t *__restrict__ dst
 }
 
 // ---------------------------------------------------------------------------------------------
+// phase-grouped bulk copy (experiment: does separating reads from writes in time help the DRAM?)
+// ---------------------------------------------------------------------------------------------
+// One CTA per SM, S stages of `chunk` bytes of shared memory each.  All CTAs of the GPU load while
+// (globaltimer / phase_ns) is even and store while it is odd, so that -- as far as the SMs can arrange it -- the
+// memory system sees T nanoseconds of reads followed by T nanoseconds of writes instead of a 50/50 mix.  Within a
+// stage index the CTAs touch one compact window of the buffers.  Waiting for a phase is bounded by the clock
+// itself (at most two phase lengths).  Measured: see the launcher.
+__device__ __forceinline__ void wait_for_phase(unsigned long long phase_ns, unsigned int want) {
+    if (phase_ns == 0) return;
+    unsigned long long t0, t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    t = t0;
+    while (((t / phase_ns) & 1ull) != want && t - t0 < 2 * phase_ns) {
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    }
+}
+
+template <int S>
+__global__ void __launch_bounds__(32) copy_phase_kernel(uint8_t *__restrict__ dst, const uint8_t *__restrict__ src, size_t body,
+                                                        uint32_t chunk, unsigned long long phase_ns, Edges e) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)S * chunk);
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) mbar_init(smem_addr(bars) + 8 * s, 1);
+        mbar_init_fence();
+    }
+    pdl_wait();
+    if (blockIdx.x == 0 && threadIdx.x != 0) {
+        const int t = threadIdx.x;
+        if (t < 16) {
+            if (t - 1 < e.head) e.dst[t - 1] = e.src[t - 1];
+        } else if (t - 16 < e.tail) {
+            e.dst[e.tail_off + (t - 16)] = e.src[e.tail_off + (t - 16)];
+        }
+    }
+    if (threadIdx.x != 0) return;
+    const size_t nchunks = (body + chunk - 1) / chunk;
+    const size_t per_round = (size_t)gridDim.x * S;
+    const uint32_t smem_base = smem_addr(smem), bar_base = smem_addr(bars);
+    uint32_t parity = 0;
+    bool ok = true;
+    for (size_t first = 0; first < nchunks && ok; first += per_round) {
+        int loaded = 0;
+        wait_for_phase(phase_ns, 0);
+        for (int s = 0; s < S; ++s) {
+            const size_t c = first + (size_t)s * gridDim.x + blockIdx.x;
+            if (c >= nchunks) break;
+            const size_t off = c * chunk;
+            const uint32_t len = body - off < chunk ? (uint32_t)(body - off) : chunk;
+            mbar_expect_tx(bar_base + 8 * s, len);
+            bulk_g2s<false>(smem_base + s * chunk, src + off, len, bar_base + 8 * s, 0);
+            ++loaded;
+        }
+        for (int s = 0; s < loaded; ++s) {
+            if (!mbar_wait_bounded(bar_base + 8 * s, parity)) {
+                ok = false;
+                break;
+            }
+        }
+        if (!ok) break;
+        wait_for_phase(phase_ns, 1);
+        for (int s = 0; s < loaded; ++s) {
+            const size_t off = (first + (size_t)s * gridDim.x + blockIdx.x) * chunk;
+            const uint32_t len = body - off < chunk ? (uint32_t)(body - off) : chunk;
+            bulk_s2g<false>(dst + off, smem_base + s * chunk, len, 0);
+        }
+        bulk_commit();
+        bulk_wait_read<0>();
+        parity ^= 1;  // every barrier that was used completed one phase; unused ones are never waited on again
+        if (loaded < S) break;  // the last, partial round
+    }
+    if (!ok) raise_error(kErrMbarrierTimeout);
+    bulk_wait_all();
+}
+
+// ---------------------------------------------------------------------------------------------
 // all-to-all (push and pull)
 // ---------------------------------------------------------------------------------------------
 struct PeerPtrs {
@@ -448,6 +525,33 @@ __global__ void __launch_bounds__(512) alltoall_kernel(PeerPtrs peers, uint4 *__
             if (j < chunk_vec) st_stream<1>(d + j, v[u]);
         }
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// flags between GPUs (one thread each): how ranks that live in different processes keep a schedule of
+// copy-engine transfers in lock-step without the host
+// ---------------------------------------------------------------------------------------------
+__global__ void flag_post_kernel(unsigned int *flag, unsigned int value) {
+    // everything earlier on the stream (the engine copy this announces) has completed before this kernel starts
+    asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(flag), "r"(value) : "memory");
+}
+
+// Returns when *flag has reached `value` (counters only grow; the comparison survives wrap-around), or after
+// `timeout_ns` of GPU time: then it raises kErrFlagTimeout in the sticky error word and returns all the same,
+// so a peer that died or never posts costs a bounded wait and an error status, not a hung GPU.
+__global__ void flag_wait_kernel(const unsigned int *flag, unsigned int value, unsigned long long timeout_ns) {
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (unsigned int polls = 0; polls < (1u << 26); ++polls) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if ((int)(v - value) >= 0) return;
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (now - t0 > timeout_ns) break;
+        __nanosleep(100);
+    }
+    raise_error(kErrFlagTimeout);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -665,6 +769,31 @@ int launch_tma2_cfg(bool hint, int grid, size_t smem, cudaStream_t st, uint8_t *
     return launch_kernel(copy_tma2_kernel<S, D, false>, grid, 64, smem, st, d, s, body, chunk, e);
 }
 
+// Phase-grouped copy (LCB_COPY_PHASED).  Not reachable from LCB_COPY_AUTO: see the measurements in the design notes.
+int launch_phased(const Split &sp, int ctas, cudaStream_t st) {
+    const Tuning &tu = tuning();
+    const uint32_t chunk = (uint32_t)tu.phase_chunk;
+    const int S = tu.phase_stages;
+    if (chunk < 1024 || chunk > 65536 || (chunk & 127)) return 1;
+    const size_t smem = (size_t)S * chunk + 8 * (size_t)S;
+    if (smem > 227 * 1024) return 1;
+    const size_t body = sp.nvec * 16;
+    const size_t nchunks = (body + chunk - 1) / chunk;
+    const size_t cap = ctas > 0 ? (size_t)ctas : (size_t)sm_count();
+    const int grid = (int)(nchunks < cap ? (nchunks ? nchunks : 1) : cap);
+    uint8_t *d = reinterpret_cast<uint8_t *>(sp.dstv);
+    const unsigned long long phase_ns = (unsigned long long)tu.phase_ns;
+    switch (S) {
+        case 2: return launch_kernel(copy_phase_kernel<2>, grid, 32, smem, st, d, sp.src_body, body, chunk, phase_ns, sp.e);
+        case 3: return launch_kernel(copy_phase_kernel<3>, grid, 32, smem, st, d, sp.src_body, body, chunk, phase_ns, sp.e);
+        case 4: return launch_kernel(copy_phase_kernel<4>, grid, 32, smem, st, d, sp.src_body, body, chunk, phase_ns, sp.e);
+        case 6: return launch_kernel(copy_phase_kernel<6>, grid, 32, smem, st, d, sp.src_body, body, chunk, phase_ns, sp.e);
+        case 12: return launch_kernel(copy_phase_kernel<12>, grid, 32, smem, st, d, sp.src_body, body, chunk, phase_ns, sp.e);
+        case 24: return launch_kernel(copy_phase_kernel<24>, grid, 32, smem, st, d, sp.src_body, body, chunk, phase_ns, sp.e);
+        default: return 1;
+    }
+}
+
 int launch_tma2(const Split &sp, int ctas, cudaStream_t st) {
     const Tuning &tu = tuning();
     const uint32_t chunk = (uint32_t)tu.tma2_chunk;
@@ -762,6 +891,9 @@ int copy_dispatch(void *dst, const void *src, size_t bytes, int path_and_flags, 
         case LCB_COPY_TMA2:
             if (!mutual || plan != nullptr) return 1;
             return launch_tma2(sp, ctas, st);
+        case LCB_COPY_PHASED:
+            if (!mutual || plan != nullptr) return 1;
+            return launch_phased(sp, ctas, st);
         case LCB_COPY_VEC32:
             if (((reinterpret_cast<uintptr_t>(dst) ^ reinterpret_cast<uintptr_t>(src)) & 31) != 0 || plan != nullptr) return 1;
             return launch_vec32(dst, src, bytes, ctas, st);
@@ -830,6 +962,57 @@ extern "C" int lcb_alltoall_push(void *const *peer_recv, const void *send, size_
 extern "C" int lcb_alltoall_pull(void *const *peer_send, void *recv, size_t chunk_bytes, int n_ranks, int rank,
                                  lcbStream stream) {
     return lcb::launch_alltoall(true, peer_send, recv, chunk_bytes, n_ranks, rank, stream);
+}
+
+extern "C" int lcb_flag_post(void *flag, unsigned int value, lcbStream stream) {
+    if (flag == nullptr || (reinterpret_cast<uintptr_t>(flag) & 3)) return 1;
+    lcb::NoPdlScope plain(true);  // must not start before the work it announces has finished
+    return lcb::launch_kernel(lcb::flag_post_kernel, 1, 1, 0, static_cast<cudaStream_t>(stream), static_cast<unsigned int *>(flag), value);
+}
+
+extern "C" int lcb_flag_wait(const void *flag, unsigned int value, unsigned int timeout_ms, lcbStream stream) {
+    if (flag == nullptr || (reinterpret_cast<uintptr_t>(flag) & 3)) return 1;
+    if (timeout_ms == 0 || timeout_ms > 10000u) return 1;  // a wait is always bounded, and by seconds at most
+    lcb::NoPdlScope plain(true);
+    return lcb::launch_kernel(lcb::flag_wait_kernel, 1, 1, 0, static_cast<cudaStream_t>(stream), static_cast<const unsigned int *>(flag),
+                              value, (unsigned long long)timeout_ms * 1000000ull);
+}
+
+extern "C" int lcb_alltoall_engines(void *const *peer_recv, const void *send, size_t chunk_bytes, int n_ranks, int rank,
+                                    void *flags, void *const *peer_flags, unsigned int epoch, unsigned int timeout_ms,
+                                    lcbStream stream, lcbStream local_stream) {
+    if (n_ranks < 1 || n_ranks > 16 || rank < 0 || rank >= n_ranks || peer_recv == nullptr || send == nullptr) return 1;
+    if (n_ranks > 2 && (flags == nullptr || peer_flags == nullptr || epoch == 0)) return 1;
+    if (chunk_bytes == 0) return 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint8_t *s = static_cast<const uint8_t *>(send);
+    unsigned int *mine = static_cast<unsigned int *>(flags);
+    const int n = n_ranks;
+    // the chunk that stays on this GPU: the copy kernel, on the second stream if one was given
+    int rc = lcb_copy_d2d(static_cast<uint8_t *>(peer_recv[rank]) + (size_t)rank * chunk_bytes, s + (size_t)rank * chunk_bytes,
+                          chunk_bytes, local_stream != nullptr ? local_stream : stream);
+    if (rc != 0) return rc;
+    for (int step = 1; step < n; ++step) {
+        const int j = (rank + step) % n;
+        if (n > 2) {
+            // GPU j must be free of its previous sender: rank+1 at the step before, or -- for the first step --
+            // rank+2 at the last step of the call before this one
+            if (step > 1) rc = lcb_flag_wait(mine + (step - 1), epoch, timeout_ms, stream);
+            else if (epoch > 1) rc = lcb_flag_wait(mine + (n - 1), epoch - 1, timeout_ms, stream);
+            if (rc != 0) return rc;
+        }
+        cudaError_t err = cudaMemcpyAsync(static_cast<uint8_t *>(peer_recv[j]) + (size_t)rank * chunk_bytes, s + (size_t)j * chunk_bytes,
+                                          chunk_bytes, cudaMemcpyDefault, st);
+        if (err != cudaSuccess) return (int)err;
+        if (n > 2) {
+            const int back = step + 1 < n ? 1 : 2;  // who waits for this copy: rank-1 (next step) or rank-2 (next call)
+            unsigned int *theirs = static_cast<unsigned int *>(peer_flags[(rank - back + 2 * n) % n]);
+            if (theirs == nullptr) return 1;
+            rc = lcb_flag_post(theirs + step, epoch, stream);
+            if (rc != 0) return rc;
+        }
+    }
+    return 0;
 }
 
 namespace lcb {

@@ -45,6 +45,9 @@ static const Tuning kDefaults = {
         /*bcast_piece_mib*/ 64,
         /*bcast_pull_ctas*/ 74,
         /*bcast_engine_piece_mib*/ 0,
+        /*phase_chunk*/ 32768,
+        /*phase_stages*/ 6,
+        /*phase_ns*/ 4000,
         /*bcast_mc_piece_mib*/ 256,
         /*bcast_mc_slots*/ 2,
         /*bcast_mc_ctas*/ 64,
@@ -88,7 +91,9 @@ static bool knob_value_ok(const char *name, int v) {
     if (is("memset_unroll")) return v == 1 || v == 2 || v == 4 || v == 8;
     if (is("copy_cache_mode")) return v >= 0 && v <= 4;
     if (is("tma_chunk") && v == 0) return true;  // 0: chunk, stages and lookahead chosen by size
-    if (is("tma_chunk") || is("tma2_chunk") || is("memset_chunk")) return v >= 1024 && v <= 65536 && (v & 127) == 0;
+    if (is("phase_stages")) return v == 2 || v == 3 || v == 4 || v == 6 || v == 12 || v == 24;
+    if (is("phase_ns")) return v >= 0 && v <= 1000000;
+    if (is("tma_chunk") || is("tma2_chunk") || is("memset_chunk") || is("phase_chunk")) return v >= 1024 && v <= 65536 && (v & 127) == 0;
     if (is("tma_stages")) return v >= 2 && v <= 16;
     if (is("tma_lookahead")) return v >= 1 && v <= 12;
     if (is("tma2_stages")) return v >= 4 && v <= 24;
@@ -154,6 +159,9 @@ int check_launch() { return (int)cudaGetLastError(); }
     X(bcast_piece_mib) \
     X(bcast_pull_ctas) \
     X(bcast_engine_piece_mib) \
+    X(phase_chunk) \
+    X(phase_stages) \
+    X(phase_ns) \
     X(bcast_mc_piece_mib) \
     X(bcast_mc_slots) \
     X(bcast_mc_ctas)

@@ -224,6 +224,32 @@ def test_bounded_wait_gives_up_with_an_error_status_and_the_device_stays_usable(
     _run_cases(stream, [(5 * MiB + 48, 16, 16)], TMA)
 
 
+def test_flag_wait_is_bounded_and_flag_post_releases_it(stream):
+    # the wait that keeps copy-engine schedules of different GPUs in step: satisfied by a post, and -- when nobody
+    # posts -- over after its time limit with bit 1 of the error word, the device fully usable afterwards
+    import time
+    flag = api.DeviceBuffer(4096)
+    stream.memset_d8(flag, 0, 4096)
+    stream.run()
+    lib = api.lib
+    assert lib.lcb_flag_wait(flag.ptr, 1, 0, stream.native) == 1            # a limit is mandatory ...
+    assert lib.lcb_flag_wait(flag.ptr, 1, 60000, stream.native) == 1        # ... and at most ten seconds
+    assert lib.lcb_flag_wait(flag.ptr + 2, 1, 100, stream.native) == 1      # misaligned word
+    api.lcb_check(lib.lcb_flag_post(flag.ptr + 8, 7, stream.native), "post")
+    api.lcb_check(lib.lcb_flag_wait(flag.ptr + 8, 7, 1000, stream.native), "wait")   # already there
+    api.lcb_check(lib.lcb_flag_wait(flag.ptr + 8, 5, 1000, stream.native), "wait")   # counters only grow
+    api.lcb_check(lib.lcb_stream_synchronize(stream.native), "sync")
+    assert api.device_error_word() == 0
+    t0 = time.perf_counter()
+    api.lcb_check(lib.lcb_flag_wait(flag.ptr + 8, 8, 150, stream.native), "wait")    # nobody posts 8
+    api.lcb_check(lib.lcb_stream_synchronize(stream.native), "sync")
+    assert 0.1 < time.perf_counter() - t0 < 1.0
+    assert api.device_error_word() == 2      # reported ...
+    assert api.device_error_word() == 0      # ... and cleared
+    _run_cases(stream, [(3 * MiB + 5, 0, 0)], AUTO)   # copies still work afterwards
+    flag.free()
+
+
 def test_device_helpers_agree_with_oracle(stream):
     n = 3 * MiB + 5
     buf, res = api.DeviceBuffer(n + 8), api.DeviceBuffer(16)
@@ -324,8 +350,11 @@ def test_host_window_check_catches_one_wrong_byte_past_4_gib(stream):
             w[planted_at - off] ^= 0x01
         return w
 
+    def only_windows_over_the_plant(bad):
+        return STRADDLE[0] in bad and all(w <= planted_at < w + (16 << 20) for w in bad)
+
     assert host_window_mismatches(stream, dst.ptr, n, truth, salt=3, extra_offsets=STRADDLE) == []
-    assert host_window_mismatches(stream, dst.ptr, n, planted, salt=3, extra_offsets=STRADDLE) == [STRADDLE[0]]
+    assert only_windows_over_the_plant(host_window_mismatches(stream, dst.ptr, n, planted, salt=3, extra_offsets=STRADDLE))
     # and a wrong byte on the DEVICE side at the same place is caught the same way
     flip = np.array([0], np.uint8)
     stream.memcpy(flip, dst.ptr + planted_at, 1)
@@ -333,6 +362,6 @@ def test_host_window_check_catches_one_wrong_byte_past_4_gib(stream):
     flip ^= 0x80
     stream.memcpy(dst.ptr + planted_at, flip, 1)
     stream.run()
-    assert host_window_mismatches(stream, dst.ptr, n, truth, salt=3, extra_offsets=STRADDLE) == [STRADDLE[0]]
+    assert only_windows_over_the_plant(host_window_mismatches(stream, dst.ptr, n, truth, salt=3, extra_offsets=STRADDLE))
     src.free()
     dst.free()

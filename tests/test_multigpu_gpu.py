@@ -229,6 +229,49 @@ def test_all_to_all_recorded_per_rank(gpus, pull):
     ctxs[0].set_current()
 
 
+def test_lockstep_engine_all_to_all_per_rank(gpus):
+    # lcb_alltoall_engines is the form for one process per GPU; here every "rank" is a stream on its own GPU of this
+    # process.  Three calls in a row with growing epochs: the flags posted by one call gate the first step of the
+    # next.  (With two GPUs there is nothing to keep in step and no flag is touched.)
+    ctxs, streams = gpus
+    G = len(ctxs)
+    chunk = 5 * MiB + 16
+    send, recv, flags = [], [], []
+    for g in range(G):
+        send.append(_alloc_on(ctxs[g], G * chunk))
+        recv.append(_alloc_on(ctxs[g], G * chunk))
+        flags.append(_alloc_on(ctxs[g], 4096))
+        _upload(ctxs, streams, g, flags[g], np.zeros(4096, np.uint8))
+    rp = (C.c_void_p * G)(*[b.ptr for b in recv])
+    fp = (C.c_void_p * G)(*[b.ptr for b in flags])
+    for epoch in (1, 2, 3):
+        send_h = [oracle.random_bytes(G * chunk, seed=90 + 10 * epoch + r) for r in range(G)]
+        want = oracle.alltoall(send_h)
+        for g in range(G):
+            _upload(ctxs, streams, g, send[g], send_h[g])
+            _upload(ctxs, streams, g, recv[g], np.zeros(G * chunk, np.uint8))
+        for g in range(G):
+            ctxs[g].set_current()
+            api.lcb_check(lib.lcb_alltoall_engines(rp, send[g].ptr, chunk, G, g, flags[g].ptr, fp, epoch, 2000,
+                                                   streams[g].native, None), "lcb_alltoall_engines")
+        for g in range(G):
+            ctxs[g].set_current()
+            api.lcb_check(lib.lcb_stream_synchronize(streams[g].native), "sync")
+            assert api.device_error_word() == 0, f"rank {g}: a flag wait ran out"
+        for g in range(G):
+            assert np.array_equal(_download(ctxs, streams, g, recv[g], G * chunk), want[g]), f"epoch {epoch} rank {g}"
+    ctxs[0].set_current()
+    assert lib.lcb_alltoall_engines(rp, send[0].ptr, chunk, G, G, flags[0].ptr, fp, 1, 2000, streams[0].native, None) == 1
+    if G > 2:
+        assert lib.lcb_alltoall_engines(rp, send[0].ptr, chunk, G, 0, None, fp, 1, 2000, streams[0].native, None) == 1
+        assert lib.lcb_alltoall_engines(rp, send[0].ptr, chunk, G, 0, flags[0].ptr, fp, 0, 2000, streams[0].native, None) == 1
+    for g in range(G):
+        ctxs[g].set_current()
+        for b in (send[g], recv[g], flags[g]):
+            b.free()
+    ctxs[0].set_current()
+
+
 @pytest.mark.parametrize("use_nccl", [0, 1, 2, 3])
 @pytest.mark.parametrize("root", [0, 1])
 def test_broadcast(gpus, use_nccl, root):
