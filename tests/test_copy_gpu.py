@@ -15,7 +15,7 @@ from gpu_util import (GUARD, GUARD_BYTE, device_checksum, device_compare, host_w
 
 pytestmark = pytest.mark.gpu
 MiB = 1 << 20
-AUTO, VEC, TMA, SMALL, VEC32, TMA2 = 0, 1, 2, 3, 4, 5
+AUTO, VEC, TMA, SMALL, VEC32, TMA2, PHASED = 0, 1, 2, 3, 4, 5, 6
 SRC_STABLE, NO_PDL = 0x100, 0x200   # flags OR'ed into the path argument
 GOLDEN = json.loads((Path(__file__).parent / "golden" / "ref_d2d_golden.json").read_text())
 
@@ -82,10 +82,10 @@ def test_all_sixteen_by_sixteen_phase_pairs(stream):
     _run_cases(stream, [(70000 + so, so, do) for so in range(16) for do in range(16)], AUTO)
 
 
-@pytest.mark.parametrize("path", [AUTO, VEC, TMA, TMA2])
+@pytest.mark.parametrize("path", [AUTO, VEC, TMA, TMA2, PHASED])
 def test_mid_and_large_sizes(stream, path):
     sizes = [MiB - 1, MiB, MiB + 131, 2 * MiB + 5, 3 * MiB + 4099, 16 * MiB + 4100, 64 * MiB + 17]
-    offs = [(0, 0), (64, 64), (16, 48)] if path in (TMA, TMA2) else [(0, 0), (1, 0), (0, 3), (7, 7), (64, 1), (3, 64), (5, 9)]
+    offs = [(0, 0), (64, 64), (16, 48)] if path in (TMA, TMA2, PHASED) else [(0, 0), (1, 0), (0, 3), (7, 7), (64, 1), (3, 64), (5, 9)]
     _run_cases(stream, [(n, so, do) for n in sizes for so, do in offs], path)
 
 
@@ -121,7 +121,18 @@ def test_copy_plan_query_names_what_is_launched(stream):
     b.free()
 
 
-@pytest.mark.parametrize("path", [TMA, TMA2])
+@pytest.mark.parametrize("knobs", [dict(phase_chunk=32768, phase_stages=6, phase_ns=4000), dict(phase_chunk=8192, phase_stages=24, phase_ns=0),
+                                   dict(phase_chunk=65536, phase_stages=3, phase_ns=1000), dict(phase_chunk=4096, phase_stages=2, phase_ns=2000)])
+def test_phase_grouped_copy_configurations(stream, knobs):
+    api.tune(**knobs)
+    try:
+        cases = [(n, o, o + 16 * k) for n in (0, 1, 17, 16385, 200001, 5 * MiB + 33, 40 * MiB + 5) for o in (0, 5) for k in (0, 2)]
+        _run_cases(stream, cases, PHASED)
+    finally:
+        api.tune_reset()
+
+
+@pytest.mark.parametrize("path", [TMA, TMA2, PHASED])
 def test_bulk_path_edges_and_small_bodies(stream, path):
     # congruent but not 16-byte aligned pointers: head and tail bytes ride along with the bulk ring
     cases = [(n, o, o + 16 * k) for n in (0, 1, 15, 16, 17, 31, 33, 1000, 16384, 16385, 3 * 16384 + 7, 200001)
