@@ -1077,11 +1077,12 @@ def run_case(args):
         a1, b1 = api.DeviceBuffer(n), api.DeviceBuffer(n)
         api.lcb_check(lib.lcb_fill_splitmix64(a1.ptr, n, 2, st1.native), "fill")
         st1.run()
+        t1 = api.Timer()      # events belong to the device that is current when they are created
         ctx.set_current()
         ctx.enable_peer_access(ctx1)
+        t0 = api.Timer()
         recv = (C.c_void_p * 2)(b.ptr, b1.ptr)
         chunk = n // 2 // 16 * 16
-        t0, t1 = api.Timer(), api.Timer()
         for _ in range(args.reps):
             ctx.set_current()
             t0.start(nat)

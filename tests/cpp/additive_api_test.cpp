@@ -3,6 +3,7 @@
 // the reference's own test programs use its API (tests/memcopy/main.cpp:1-75 there): include <librecuda.h>,
 // link the `driverapi` library, check every status.  Verifies results against host computations and prints
 // "additive API ok".  Needs one GPU.
+#include <lcb200_kernels.h>
 #include <librecuda.h>
 
 #include <cstdint>
@@ -125,6 +126,30 @@ int main() {
     void *native = nullptr;
     CHECK(libreCuStreamGetNativeHandle(&native, a));
     EXPECT(native != nullptr);
+
+    // the kernel layer underneath, on the stream's native handle: the plan query names what will be launched, a
+    // copy whose source nothing in flight writes may load ahead of the stream wait, and a bounded wait that runs
+    // out shows up as the status of the next Await (once), not as a hang or a CUDA error
+    char plan[200] = {};
+    EXPECT(lcb_copy_d2d_describe(dev1, dev0, n, LCB_COPY_AUTO | LCB_COPY_SRC_STABLE, 0, plan, sizeof(plan)) == 0);
+    EXPECT(std::strstr(plan, "copy_vec_kernel<-1,") == plan && std::strstr(plan, "loads before the stream wait") != nullptr);
+    EXPECT(lcb_copy_d2d_describe(dev1, dev0 + 1, n, LCB_COPY_TMA, 0, plan, sizeof(plan)) == 1);  // bulk path needs congruent pointers
+    CHECK(libreCuMemsetD8(dev1, 0, n + 64, a));
+    CHECK(libreCuStreamCommence(a));
+    CHECK(libreCuStreamAwait(a));
+    for (int rep = 0; rep < 4; ++rep)
+        EXPECT(lcb_copy_d2d_ex(dev1 + 5, dev0 + 2, n, LCB_COPY_AUTO | LCB_COPY_SRC_STABLE, 0, native) == 0);
+    CHECK(libreCuMemcpyDtoH(pageable.data(), dev1 + 5, n, a));
+    CHECK(libreCuStreamCommence(a));
+    CHECK(libreCuStreamAwait(a));
+    EXPECT(std::memcmp(pageable.data(), pinned + 2, n) == 0);
+    EXPECT(lcb_flag_wait(dev1, 1, 0, native) == 1);                 // a wait without a limit is refused
+    EXPECT(lcb_flag_wait(dev1, 0x7fffffffu, 50, native) == 0);      // nobody posts this value: gives up after 50 ms
+    EXPECT(libreCuStreamAwait(a) == LIBRECUDA_ERROR_UNKNOWN);       // reported once ...
+    CHECK(libreCuStreamAwait(a));                                   // ... then clear, and the stream still works
+    EXPECT(lcb_flag_post(dev1, 7, native) == 0);
+    EXPECT(lcb_flag_wait(dev1, 7, 1000, native) == 0);
+    CHECK(libreCuStreamAwait(a));
 
     CHECK(libreCuEventDestroy(produced));
     CHECK(libreCuEventDestroy(start));
