@@ -121,6 +121,7 @@ LIBRECU_FUNCTIONS = {
     "libreCuMemcpyPartitioned": (i32, [vpp, vp, sz, i32, sz, vpp]),
     "libreCuAllToAllPush": (i32, [vpp, vp, sz, i32, i32, vp]),
     "libreCuAllToAllPull": (i32, [vpp, vp, sz, i32, i32, vp]),
+    "libreCuAllToAllEngines": (i32, [vpp, vp, sz, i32, i32, vpp, C.c_uint, C.c_uint, vp]),
     "libreCuAllToAll": (i32, [vpp, vpp, sz, i32, vpp, i32]),
     "libreCuBroadcast": (i32, [vpp, i32, sz, i32, vpp, i32]),
     "libreCuIpcGetMemHandle": (i32, [vp, vp]),

@@ -165,7 +165,7 @@ struct LibreCUEvent_ {
 namespace lcu {
 
 struct Command {
-    enum Kind { CopyKernel, CopyEngine, Memset, Launch, EventRecord, WaitEvent, AllToAllPush, AllToAllPull };
+    enum Kind { CopyKernel, CopyEngine, Memset, Launch, EventRecord, WaitEvent, AllToAllPush, AllToAllPull, AllToAllEngines };
     Kind kind;
     bool async = false;
     // copies / memset
@@ -182,9 +182,11 @@ struct Command {
     std::vector<unsigned char> params;  // argument values captured at record time
     // events
     LibreCUEvent event = nullptr;
-    // all-to-all push
+    // all-to-all (per-rank forms)
     std::vector<void *> peers;
     int rank = 0;
+    std::vector<void *> peer_flags;  // lock-step engine form: every rank's flag words, own ones at [rank]
+    unsigned int epoch = 0, timeout_ms = 0;
 };
 
 constexpr int kSideLanes = 8;

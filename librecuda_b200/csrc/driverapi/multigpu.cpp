@@ -126,6 +126,39 @@ libreCudaStatus_t libreCuAllToAllPull(void *const *peerSendBufs, void *recvBuf, 
     return record_alltoall(true, peerSendBufs, recvBuf, chunkBytes, nRanks, rank, stream);
 }
 
+libreCudaStatus_t libreCuAllToAllEngines(void *const *peerRecvBufs, const void *sendBuf, size_t chunkBytes, int nRanks, int rank,
+                                         void *const *peerFlags, unsigned int epoch, unsigned int timeoutMs, LibreCUstream stream) {
+    return lcu_guarded([&]() -> libreCudaStatus_t {
+        LIBRECUDA_VALIDATE(peerRecvBufs != nullptr && sendBuf != nullptr && stream != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(nRanks >= 1 && nRanks <= 16 && rank >= 0 && rank < nRanks, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(timeoutMs >= 1 && timeoutMs <= 10000, LIBRECUDA_ERROR_INVALID_VALUE);
+        if (nRanks > 2) {
+            LIBRECUDA_VALIDATE(peerFlags != nullptr && epoch >= 1, LIBRECUDA_ERROR_INVALID_VALUE);
+            for (int j = 0; j < nRanks; ++j) {
+                LIBRECUDA_VALIDATE(peerFlags[j] != nullptr && (reinterpret_cast<uintptr_t>(peerFlags[j]) & 3) == 0, LIBRECUDA_ERROR_INVALID_VALUE);
+                const int owner = owner_device(peerFlags[j]);
+                LIBRECUDA_VALIDATE(owner < 0 || stream->ctx->peers.count(owner) != 0, LIBRECUDA_ERROR_INVALID_VALUE);
+            }
+        }
+        for (int j = 0; j < nRanks; ++j) {
+            LIBRECUDA_VALIDATE(peerRecvBufs[j] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+            const int owner = owner_device(peerRecvBufs[j]);
+            LIBRECUDA_VALIDATE(owner < 0 || stream->ctx->peers.count(owner) != 0, LIBRECUDA_ERROR_INVALID_VALUE);
+        }
+        if (chunkBytes == 0) LIBRECUDA_SUCCEED();
+        Command c;
+        c.kind = Command::AllToAllEngines;
+        c.src = sendBuf;
+        c.bytes = chunkBytes;
+        c.rank = rank;
+        c.peers.assign(peerRecvBufs, peerRecvBufs + nRanks);
+        if (nRanks > 2) c.peer_flags.assign(peerFlags, peerFlags + nRanks);
+        c.epoch = epoch;
+        c.timeout_ms = timeoutMs;
+        return record(stream, std::move(c));
+    });
+}
+
 // ---- NCCL, loaded on first use ------------------------------------------------------------------------------
 namespace {
 

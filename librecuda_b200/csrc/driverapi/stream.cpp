@@ -168,6 +168,18 @@ static libreCudaStatus_t submit(LibreCUstream st, Command &c) {
             if (!c.async) st->main_writes.add(c.dst, c.bytes * c.peers.size());
             LCU_LCB(lcb_alltoall_pull(c.peers.data(), c.dst, c.bytes, (int)c.peers.size(), c.rank, lane));
             break;
+        case Command::AllToAllEngines: {
+            // engine copies on the main lane, the local chunk as a kernel on a side lane beside them
+            LIBRECUDA_ERR_PROPAGATE(pick_lane(st, false, &lane));
+            st->main_writes.clear();  // copy-engine transfers serialise the lane
+            cudaStream_t local = nullptr;
+            LIBRECUDA_ERR_PROPAGATE(fork_side(st, 0, &local));
+            LCU_LCB(lcb_alltoall_engines(c.peers.data(), c.src, c.bytes, (int)c.peers.size(), c.rank,
+                                         c.peer_flags.empty() ? nullptr : c.peer_flags[(size_t)c.rank],
+                                         c.peer_flags.empty() ? nullptr : c.peer_flags.data(), c.epoch, c.timeout_ms, lane, local));
+            st->main_writes.add_unknown();
+            break;
+        }
         case Command::Launch: {
             LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
             // a user kernel is launched without programmatic serialization: it starts after, and whatever follows

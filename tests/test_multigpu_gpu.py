@@ -272,6 +272,44 @@ def test_lockstep_engine_all_to_all_per_rank(gpus):
     ctxs[0].set_current()
 
 
+def test_lockstep_engine_all_to_all_recorded(gpus):
+    # the same exchange as a recorded stream operation (libreCuAllToAllEngines): runs at Commence, its local chunk on
+    # a side lane that the next ordered operation joins; a DtoH recorded after it sees the complete result
+    ctxs, streams = gpus
+    G = len(ctxs)
+    chunk = 2 * MiB + 32
+    send_h = [oracle.random_bytes(G * chunk, seed=120 + r) for r in range(G)]
+    want = oracle.alltoall(send_h)
+    send = [_alloc_on(ctxs[g], G * chunk) for g in range(G)]
+    recv = [_alloc_on(ctxs[g], G * chunk) for g in range(G)]
+    flags = [_alloc_on(ctxs[g], 4096) for g in range(G)]
+    rp = (C.c_void_p * G)(*[b.ptr for b in recv])
+    fp = (C.c_void_p * G)(*[b.ptr for b in flags])
+    for g in range(G):
+        _upload(ctxs, streams, g, flags[g], np.zeros(4096, np.uint8))
+        _upload(ctxs, streams, g, recv[g], np.zeros(G * chunk, np.uint8))
+    for g in range(G):
+        ctxs[g].set_current()
+        streams[g].memcpy(send[g], send_h[g], G * chunk)
+        api.check(lib.libreCuAllToAllEngines(rp, send[g].ptr, chunk, G, g, fp, 1, 2000, streams[g].handle))
+    # nothing ran yet: recorded only.  All ranks must be commenced before any is awaited (they wait for each other)
+    for s in streams:
+        s.commence()
+    for s in streams:
+        s.await_()
+    for g in range(G):
+        assert np.array_equal(_download(ctxs, streams, g, recv[g], G * chunk), want[g]), f"rank {g}"
+    ctxs[0].set_current()
+    assert lib.libreCuAllToAllEngines(rp, send[0].ptr, chunk, G, 0, fp, 1, 0, streams[0].handle) == api.ERROR_INVALID_VALUE
+    if G > 2:
+        assert lib.libreCuAllToAllEngines(rp, send[0].ptr, chunk, G, 0, None, 1, 2000, streams[0].handle) == api.ERROR_INVALID_VALUE
+    for g in range(G):
+        ctxs[g].set_current()
+        for b in (send[g], recv[g], flags[g]):
+            b.free()
+    ctxs[0].set_current()
+
+
 @pytest.mark.parametrize("use_nccl", [0, 1, 2, 3])
 @pytest.mark.parametrize("root", [0, 1])
 def test_broadcast(gpus, use_nccl, root):
