@@ -618,13 +618,11 @@ int launch_vec_unroll(int unroll, int mode, int grid, int threads, cudaStream_t 
 
 int launch_vec(const Split &sp, int ctas, bool small, cudaStream_t st, int early, Plan *plan) {
     const Tuning &tu = tuning();
-    const bool realign = (reinterpret_cast<uintptr_t>(sp.src_body) & 15) != 0;
     // Launch shape.  Measured on B200: one SHORT CTA per tile -- a grid as large as the tile count, scheduled by
     // the hardware as SMs free up -- beats a persistent grid at every size above L2 (7.0 vs 6.65 TB/s at
-    // 1 GiB).  Best tile: 128 threads x 2 vectors (4 KiB) from ~100 MiB to a few GiB, 512 x 4 (32 KiB)
-    // below that, for the realigning path and for the very largest copies (congruent pointers go to the
-    // bulk-copy kernel from 2 GiB on, see lcb_copy_d2d_ex).
-    const size_t bytes = sp.nvec * 16;
+    // 1 GiB).  Tile: 512 threads x 4 vectors (32 KiB); 128 x 2 measured 0.5-1.5 % less from 96 MiB to 1 GiB once
+    // the loads may run ahead of the stream wait.  (Congruent pointers go to the bulk-copy kernel from 96 MiB
+    // on, see copy_dispatch.)
     int threads, unroll;
     if (small) {
         threads = 128;
@@ -632,9 +630,6 @@ int launch_vec(const Split &sp, int ctas, bool small, cudaStream_t st, int early
     } else if (tu.copy_vec_threads > 0 && tu.copy_vec_unroll > 0) {
         threads = tu.copy_vec_threads;
         unroll = tu.copy_vec_unroll;
-    } else if (!realign && bytes >= ((size_t)96 << 20) && bytes <= ((size_t)4 << 30)) {
-        threads = 128;
-        unroll = 2;
     } else {
         threads = 512;
         unroll = 4;
@@ -861,6 +856,7 @@ int preload_copy_kernels() {
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<2, 4, 2>);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<3, 4, 2>);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_tma_kernel<2, 1, false>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_tma_kernel<3, 2, false>);
     return (int)e;
 }
 }  // namespace lcb

@@ -172,6 +172,6 @@ def test_copy_plan_query_follows_the_dispatcher():
     assert lib.lcb_copy_d2d_describe(4096, 1 << 40, 1 << 20, 0x400, 0, buf, 200) == 1        # unknown flag
     lib.lcb_tune(b"auto_tma_min_mib", -1)
     try:
-        assert plan(4096, 1 << 40, 1 << 30).startswith("copy_vec_kernel<-1,2,2>, 262144 CTAs x 128")
+        assert plan(4096, 1 << 40, 1 << 30).startswith("copy_vec_kernel<-1,4,2>, 32768 CTAs x 512")
     finally:
         lib.lcb_tune(b"reset", 0)
