@@ -69,9 +69,9 @@ bool resolve_epochs(std::vector<uint64_t> &base_ns, size_t &resolved, size_t upt
 // The library's kernels are launched so that the NEXT kernel's CTAs become resident while the previous one
 // drains; a copy whose source nothing in flight writes may start loading at once (LCB_COPY_SRC_STABLE).  This
 // log holds the byte ranges written by the library kernels submitted to one CUDA stream since the last
-// operation that fully serialises the stream (a copy-engine transfer, a user kernel, a host wait).  It is
-// conservative: `unknown` (a kernel whose writes are not tracked) or an overflow makes every query say "may
-// be written".
+// operation that fully serialises the stream (a copy-engine transfer, a host wait).  It is conservative:
+// `unknown` (a user kernel or a collective, whose writes are not tracked) or an overflow makes every query say
+// "may be written".
 class WriteLog {
 public:
     void clear() {
@@ -80,6 +80,9 @@ public:
     }
     void add(const void *p, size_t bytes) {
         if (bytes == 0) return;
+        const uintptr_t lo = reinterpret_cast<uintptr_t>(p), hi = lo + bytes;
+        for (int i = 0; i < n_; ++i)
+            if (lo_[i] <= lo && hi <= hi_[i]) return;  // already covered (the same buffer written again and again)
         if (n_ == kMax) {
             unknown_ = true;
             return;

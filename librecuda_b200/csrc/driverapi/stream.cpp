@@ -182,9 +182,9 @@ static libreCudaStatus_t submit(LibreCUstream st, Command &c) {
         }
         case Command::Launch: {
             LIBRECUDA_ERR_PROPAGATE(pick_lane(st, c.async, &lane));
-            // a user kernel is launched without programmatic serialization: it starts after, and whatever follows
-            // it starts behind, everything submitted before
-            if (!c.async) st->main_writes.clear();
+            // what a user kernel writes is unknown, and a library kernel behind it may become resident as soon as the
+            // user kernel's last block has exited: no loads ahead of the wait until the lane has fully serialised
+            if (!c.async) st->main_writes.add_unknown();
             LibreCUFunction f = c.fn;
             std::vector<void *> argv(f->param_size.size());
             for (size_t i = 0; i < argv.size(); ++i) argv[i] = c.params.data() + f->param_offset[i];

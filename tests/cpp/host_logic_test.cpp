@@ -75,6 +75,10 @@ int main() {
         CHECK(log.may_be_written(p + 900000, 1));
         log.clear();
         CHECK(!log.may_be_written(p + 100, 50));
+        for (int i = 0; i < 1000; ++i) log.add(p + 64, 32);  // the same range over and over takes one slot
+        for (int i = 0; i < 1000; ++i) log.add(p + 70, 8);   // and so does a part of it
+        CHECK(log.may_be_written(p + 95, 1) && !log.may_be_written(p + 96, 1000) && !log.may_be_written(p, 64));
+        log.clear();
         log.add_unknown();
         CHECK(log.may_be_written(p, 1));
         log.clear();
