@@ -443,7 +443,8 @@ def run_ours(args):
 
 
 def run_small_ops(api, stream, src, dst):
-    """Cost of tiny operations, the reference's own measurements: back-to-back small copies on one stream, and
+    """Cost of tiny operations, the reference's own measurements: back-to-back small copies on one stream (CUDA
+    events around 2 000 launches enqueued from Python: the larger of the device's and the host's cost per launch), and
     1 025 launches of an empty kernel from 1 025 modules loaded from one image
     (tests/many_kernels_launch/main.cpp:49-90: host time from the first libreCuLaunchKernel to the return of
     libreCuStreamCommence, divided by the launches; the device time between two events is reported beside it)."""
@@ -455,7 +456,7 @@ def run_small_ops(api, stream, src, dst):
         fn = lambda: api.lcb_check(lib.lcb_copy_d2d(dst.ptr, src.ptr, nb, native), "small copy")
         for _ in range(50):
             fn()
-        out[f"lcb_{label}_us_per_op_device"] = round(timed_loop(api, stream, fn, reps) * 1e3, 3)
+        out[f"lcb_{label}_us_per_op_back_to_back"] = round(timed_loop(api, stream, fn, reps) * 1e3, 3)
     # the same 4 KiB copies through the public API: record, commence, await (host clock: includes recording)
     stream.run()
     t0 = time.perf_counter()
