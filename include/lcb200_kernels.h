@@ -110,6 +110,13 @@ int lcb_alltoall_pull(void *const *peer_send, void *recv, size_t chunk_bytes, in
 int lcb_alltoall_engines(void *const *peer_recv, const void *send, size_t chunk_bytes, int n_ranks, int rank,
                          void *flags, void *const *peer_flags, unsigned int epoch, unsigned int timeout_ms,
                          lcbStream stream, lcbStream local_stream);
+/* The schedule of that exchange as a pure function (no GPU): for `step` in [1, n_ranks) of `rank` it gives the
+ * destination rank of the copy, the own flag word to wait on first (-1: none) and whether the value awaited is
+ * the previous call's epoch, and the rank and flag word to post to afterwards (-1: none).  lcb_alltoall_engines
+ * follows exactly this; the tests replay it with arbitrary copy durations to show that no GPU ever has two
+ * senders and that nobody waits for ever. */
+int lcb_alltoall_engines_step(int n_ranks, int rank, int step, int *dest, int *wait_slot, int *wait_previous_call,
+                              int *post_rank, int *post_slot);
 /* The two flag primitives it is built from.  lcb_flag_post: once everything earlier on `stream` has finished,
  * store `value` to the 4-byte aligned word `flag` (any memory this GPU may write, a peer's included).
  * lcb_flag_wait: work later on `stream` starts when the word has reached `value` (counters only grow), or

@@ -974,6 +974,32 @@ extern "C" int lcb_flag_wait(const void *flag, unsigned int value, unsigned int 
                               value, (unsigned long long)timeout_ms * 1000000ull);
 }
 
+extern "C" int lcb_alltoall_engines_step(int n_ranks, int rank, int step, int *dest, int *wait_slot, int *wait_previous_call,
+                                         int *post_rank, int *post_slot) {
+    if (n_ranks < 1 || n_ranks > 16 || rank < 0 || rank >= n_ranks || step < 1 || step >= n_ranks) return 1;
+    if (dest == nullptr || wait_slot == nullptr || wait_previous_call == nullptr || post_rank == nullptr || post_slot == nullptr) return 1;
+    const int n = n_ranks;
+    *dest = (rank + step) % n;
+    *wait_slot = -1;
+    *wait_previous_call = 0;
+    *post_rank = -1;
+    *post_slot = -1;
+    if (n <= 2) return 0;  // one peer: nothing to keep in step
+    // GPU `dest` must be free of its previous sender: rank+1 at the step before, or -- for the first step -- rank+2
+    // at the last step of the call before this one
+    if (step > 1) {
+        *wait_slot = step - 1;
+    } else {
+        *wait_slot = n - 1;
+        *wait_previous_call = 1;
+    }
+    // who waits for THIS copy: rank-1 (at its next step) or, after the last step, rank-2 (at the next call's first)
+    const int back = step + 1 < n ? 1 : 2;
+    *post_rank = (rank - back + 2 * n) % n;
+    *post_slot = step;
+    return 0;
+}
+
 extern "C" int lcb_alltoall_engines(void *const *peer_recv, const void *send, size_t chunk_bytes, int n_ranks, int rank,
                                     void *flags, void *const *peer_flags, unsigned int epoch, unsigned int timeout_ms,
                                     lcbStream stream, lcbStream local_stream) {
@@ -989,22 +1015,20 @@ extern "C" int lcb_alltoall_engines(void *const *peer_recv, const void *send, si
                           chunk_bytes, local_stream != nullptr ? local_stream : stream);
     if (rc != 0) return rc;
     for (int step = 1; step < n; ++step) {
-        const int j = (rank + step) % n;
-        if (n > 2) {
-            // GPU j must be free of its previous sender: rank+1 at the step before, or -- for the first step --
-            // rank+2 at the last step of the call before this one
-            if (step > 1) rc = lcb_flag_wait(mine + (step - 1), epoch, timeout_ms, stream);
-            else if (epoch > 1) rc = lcb_flag_wait(mine + (n - 1), epoch - 1, timeout_ms, stream);
+        int j, wait_slot, wait_prev, post_rank, post_slot;
+        rc = lcb_alltoall_engines_step(n, rank, step, &j, &wait_slot, &wait_prev, &post_rank, &post_slot);
+        if (rc != 0) return rc;
+        if (wait_slot >= 0 && !(wait_prev && epoch == 1)) {  // the very first call has no call before it
+            rc = lcb_flag_wait(mine + wait_slot, wait_prev ? epoch - 1 : epoch, timeout_ms, stream);
             if (rc != 0) return rc;
         }
         cudaError_t err = cudaMemcpyAsync(static_cast<uint8_t *>(peer_recv[j]) + (size_t)rank * chunk_bytes, s + (size_t)j * chunk_bytes,
                                           chunk_bytes, cudaMemcpyDefault, st);
         if (err != cudaSuccess) return (int)err;
-        if (n > 2) {
-            const int back = step + 1 < n ? 1 : 2;  // who waits for this copy: rank-1 (next step) or rank-2 (next call)
-            unsigned int *theirs = static_cast<unsigned int *>(peer_flags[(rank - back + 2 * n) % n]);
+        if (post_rank >= 0) {
+            unsigned int *theirs = static_cast<unsigned int *>(peer_flags[post_rank]);
             if (theirs == nullptr) return 1;
-            rc = lcb_flag_post(theirs + step, epoch, stream);
+            rc = lcb_flag_post(theirs + post_slot, epoch, stream);
             if (rc != 0) return rc;
         }
     }
