@@ -85,3 +85,20 @@ def test_two_ranks_need_no_flags_and_bad_arguments_are_refused():
     assert N.lib.lcb_alltoall_engines_step(4, 0, 4, *refs) == 1
     assert N.lib.lcb_alltoall_engines_step(4, 4, 1, *refs) == 1
     assert N.lib.lcb_alltoall_engines_step(17, 0, 1, *refs) == 1
+
+
+def test_the_simulation_sees_collisions_when_the_flags_are_ignored(monkeypatch):
+    # the same replay with every wait and post removed (what the unsynchronised engine schedule did): receivers do
+    # get two senders at once, so a pass of the test above is not vacuous
+    import sys
+
+    me = sys.modules[__name__]
+    real = me.step_plan
+    monkeypatch.setattr(me, "step_plan", lambda n, r, s: [real(n, r, s)[0], -1, 0, -1, -1])
+    done, intervals, _ = simulate(5, 3, random.Random(1))
+    assert len(done) == 5
+    overlaps = 0
+    for spans in intervals.values():
+        spans.sort()
+        overlaps += sum(1 for a, b in zip(spans, spans[1:]) if b[0] < a[1] - 1e-12)
+    assert overlaps > 0
