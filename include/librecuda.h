@@ -228,7 +228,8 @@ LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAllEngines(void *const *peerRecvB
 // libreCuBroadcast also takes useNccl == 3: NVLink multicast.  The root writes its buffer once with multimem
 // stores to a multicast address, NVSwitch delivers a copy into a staging slab of the library on every GPU, and
 // each GPU copies the pieces from its slab into its buffer; nothing is forwarded by a GPU, so the rate does not
-// drop with the number of GPUs.  The buffers themselves can be any device memory (any alignment on the
+// drop with the number of GPUs (measured 527-552 GB/s at 2 and 4 GPUs: multicast writes of one GPU are capped there,
+// below the engine chain of form 2 at those counts).  The buffers themselves can be any device memory (any alignment on the
 // receivers; a root buffer that is not 16-byte aligned, or GPUs without multicast support, take form 2 -- form 0
 // with two GPUs -- instead).  The slabs (512 MiB per GPU by default) are created at the first call for a group
 // of devices and released by libreCuCtxDestroy of any of them, or at exit.
