@@ -789,7 +789,7 @@ def run_nvlink(api, stream, rank, world, dist, torch, steps, barrier, max_over_r
     def a2a_engines():
         epoch[0] += 1
         api.lcb_check(lib.lcb_stream_wait_stream(side.native, native), "fork")
-        api.lcb_check(lib.lcb_alltoall_engines(peer_arr, send.ptr, chunk, G, rank, flags.ptr, flag_arr, epoch[0], 2000,
+        api.lcb_check(lib.lcb_alltoall_engines(peer_arr, send.ptr, chunk, G, rank, flags.ptr, flag_arr, epoch[0], 250,
                                                native, side.native), "a2a engines")
         api.lcb_check(lib.lcb_stream_wait_stream(native, side.native), "join")
 

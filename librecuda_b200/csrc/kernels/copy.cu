@@ -539,7 +539,21 @@ __global__ void flag_post_kernel(unsigned int *flag, unsigned int value) {
 // Returns when *flag has reached `value` (counters only grow; the comparison survives wrap-around), or after
 // `timeout_ns` of GPU time: then it raises kErrFlagTimeout in the sticky error word and returns all the same,
 // so a peer that died or never posts costs a bounded wait and an error status, not a hung GPU.
+__device__ __forceinline__ void flag_wait(const unsigned int *flag, unsigned int value, unsigned long long timeout_ns);
+
 __global__ void flag_wait_kernel(const unsigned int *flag, unsigned int value, unsigned long long timeout_ns) {
+    flag_wait(flag, value, timeout_ns);
+}
+
+// Post one flag, then wait for another, in one launch: between two engine copies of the lock-step exchange this
+// saves a kernel launch and an engine-kernel switch.
+__global__ void flag_post_wait_kernel(unsigned int *post, unsigned int post_value, const unsigned int *flag, unsigned int value,
+                                      unsigned long long timeout_ns) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(post), "r"(post_value) : "memory");
+    flag_wait(flag, value, timeout_ns);
+}
+
+__device__ __forceinline__ void flag_wait(const unsigned int *flag, unsigned int value, unsigned long long timeout_ns) {
     unsigned long long t0;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     for (unsigned int polls = 0; polls < (1u << 26); ++polls) {
@@ -1014,25 +1028,35 @@ extern "C" int lcb_alltoall_engines(void *const *peer_recv, const void *send, si
     int rc = lcb_copy_d2d(static_cast<uint8_t *>(peer_recv[rank]) + (size_t)rank * chunk_bytes, s + (size_t)rank * chunk_bytes,
                           chunk_bytes, local_stream != nullptr ? local_stream : stream);
     if (rc != 0) return rc;
+    if (timeout_ms == 0 || timeout_ms > 10000u) return 1;
+    unsigned int *owed = nullptr;  // the post that announces the copy just issued; goes out with the next wait
     for (int step = 1; step < n; ++step) {
         int j, wait_slot, wait_prev, post_rank, post_slot;
         rc = lcb_alltoall_engines_step(n, rank, step, &j, &wait_slot, &wait_prev, &post_rank, &post_slot);
         if (rc != 0) return rc;
-        if (wait_slot >= 0 && !(wait_prev && epoch == 1)) {  // the very first call has no call before it
-            rc = lcb_flag_wait(mine + wait_slot, wait_prev ? epoch - 1 : epoch, timeout_ms, stream);
-            if (rc != 0) return rc;
+        const bool wait = wait_slot >= 0 && !(wait_prev && epoch == 1);  // the very first call has no call before it
+        const unsigned int awaited = wait_prev ? epoch - 1 : epoch;
+        if (owed != nullptr && wait) {
+            lcb::NoPdlScope plain(true);
+            rc = lcb::launch_kernel(lcb::flag_post_wait_kernel, 1, 1, 0, st, owed, epoch, static_cast<const unsigned int *>(mine + wait_slot),
+                                    awaited, (unsigned long long)timeout_ms * 1000000ull);
+        } else {
+            if (owed != nullptr) rc = lcb_flag_post(owed, epoch, stream);
+            if (rc == 0 && wait) rc = lcb_flag_wait(mine + wait_slot, awaited, timeout_ms, stream);
         }
+        if (rc != 0) return rc;
+        owed = nullptr;
         cudaError_t err = cudaMemcpyAsync(static_cast<uint8_t *>(peer_recv[j]) + (size_t)rank * chunk_bytes, s + (size_t)j * chunk_bytes,
                                           chunk_bytes, cudaMemcpyDefault, st);
         if (err != cudaSuccess) return (int)err;
         if (post_rank >= 0) {
             unsigned int *theirs = static_cast<unsigned int *>(peer_flags[post_rank]);
             if (theirs == nullptr) return 1;
-            rc = lcb_flag_post(theirs + post_slot, epoch, stream);
-            if (rc != 0) return rc;
+            owed = theirs + post_slot;
         }
     }
-    return 0;
+    if (owed != nullptr) rc = lcb_flag_post(owed, epoch, stream);
+    return rc;
 }
 
 namespace lcb {

@@ -252,7 +252,7 @@ def test_lockstep_engine_all_to_all_per_rank(gpus):
             _upload(ctxs, streams, g, recv[g], np.zeros(G * chunk, np.uint8))
         for g in range(G):
             ctxs[g].set_current()
-            api.lcb_check(lib.lcb_alltoall_engines(rp, send[g].ptr, chunk, G, g, flags[g].ptr, fp, epoch, 2000,
+            api.lcb_check(lib.lcb_alltoall_engines(rp, send[g].ptr, chunk, G, g, flags[g].ptr, fp, epoch, 500,
                                                    streams[g].native, None), "lcb_alltoall_engines")
         for g in range(G):
             ctxs[g].set_current()
@@ -291,7 +291,7 @@ def test_lockstep_engine_all_to_all_recorded(gpus):
     for g in range(G):
         ctxs[g].set_current()
         streams[g].memcpy(send[g], send_h[g], G * chunk)
-        api.check(lib.libreCuAllToAllEngines(rp, send[g].ptr, chunk, G, g, fp, 1, 2000, streams[g].handle))
+        api.check(lib.libreCuAllToAllEngines(rp, send[g].ptr, chunk, G, g, fp, 1, 500, streams[g].handle))
     # nothing ran yet: recorded only.  All ranks must be commenced before any is awaited (they wait for each other)
     for s in streams:
         s.commence()
