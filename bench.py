@@ -204,7 +204,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": "dtod_copy_1GiB_aligned", "bytes": n, "seed": 1,
+        "config": {"workload": "dtod_copy_1GiB_aligned", "bytes_per_gpu": n, "bytes": n, "seed": 1,
+                   "algorithmic_bytes_per_step_per_gpu": 2 * n,
                    "note": "reference's CPU statement of the path: multithreaded memcpy of the same seeded bytes"},
         "cpu_baseline": {"value": round(value, 2), "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": f"{args.steps} x memcpy of 1 GiB split over {threads} threads"},
