@@ -1007,7 +1007,9 @@ def run_one_process(api, ctx0, G, reps):
             out[name] = {"error": str(exc)}
             continue
         ok = all(holds_stream(g, bufs[g].ptr, bsz, 3, 0, salt=71 + g) for g in range(G))
-        out[name] = entry(bsz / (ms * 1e-3) / 1e9, ms, ok)
+        ran = C.c_int(-1)
+        api.check(lib.libreCuBroadcastLastForm(C.byref(ran)), "libreCuBroadcastLastForm")
+        out[name] = entry(bsz / (ms * 1e-3) / 1e9, ms, ok, form_that_ran=ran.value)
     for g in range(G):
         on(g)
         bufs[g].free()

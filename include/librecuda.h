@@ -235,6 +235,9 @@ LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAllEngines(void *const *peerRecvB
 // of devices and released by libreCuCtxDestroy of any of them, or at exit.
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, size_t chunkBytes, int nDev, const LibreCUstream *streams, int useNccl);
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount, int nDev, const LibreCUstream *streams, int useNccl);
+// The form the most recent libreCuBroadcast of this process actually ran (0..3; -1 before the first call): a
+// request for form 3 runs as 2 or 0 when multicast is not available or the root buffer is not 16-byte aligned.
+LIBRECUDA_EXPORT libreCudaStatus_t libreCuBroadcastLastForm(int *pFormOut);
 
 // Inter-process sharing of a libreCuMemAlloc allocation (one process per GPU).  `handle` points at
 // LIBRECUDA_IPC_HANDLE_SIZE bytes that the exporting process sends to its peers by any means.

@@ -125,6 +125,7 @@ LIBRECU_FUNCTIONS = {
     "libreCuAllToAllEngines": (i32, [vpp, vp, sz, i32, i32, vpp, C.c_uint, C.c_uint, vp]),
     "libreCuAllToAll": (i32, [vpp, vpp, sz, i32, vpp, i32]),
     "libreCuBroadcast": (i32, [vpp, i32, sz, i32, vpp, i32]),
+    "libreCuBroadcastLastForm": (i32, [C.POINTER(i32)]),
     "libreCuIpcGetMemHandle": (i32, [vp, vp]),
     "libreCuIpcOpenMemHandle": (i32, [vpp, vp]),
     "libreCuIpcCloseMemHandle": (i32, [vp]),

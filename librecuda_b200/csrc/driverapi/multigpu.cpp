@@ -475,6 +475,16 @@ libreCudaStatus_t bcast_multicast(void *const *bufs, int root, size_t lo, size_t
 
 }  // namespace
 
+namespace {
+int g_last_broadcast_form = -1;  // the form the most recent libreCuBroadcast really ran (after any fall-back)
+}
+
+libreCudaStatus_t libreCuBroadcastLastForm(int *pFormOut) {
+    LIBRECUDA_VALIDATE(pFormOut != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
+    *pFormOut = g_last_broadcast_form;
+    LIBRECUDA_SUCCEED();
+}
+
 libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount, int nDev, const LibreCUstream *streams,
                                    int useNccl) {
     return lcu_guarded([&]() -> libreCudaStatus_t {
@@ -508,6 +518,7 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
                 LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
                 LIBRECUDA_ERR_PROPAGATE(bcast_multicast(bufs, root, 0, byteCount, nDev, streams, mains, win, piece, slots));
                 LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+                g_last_broadcast_form = 3;
                 return rebind_current();
             }
             useNccl = nDev == 2 ? 0 : 2;
@@ -516,6 +527,7 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
             LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
             LIBRECUDA_ERR_PROPAGATE(bcast_chain(bufs, root, 0, byteCount, nDev, streams, mains));
             LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+            g_last_broadcast_form = 2;
             return rebind_current();
         }
         if (useNccl == 1) {
@@ -530,8 +542,10 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
             for (int r = 0; r < nDev; ++r)
                 LCU_NCCL(n, n->Broadcast(bufs[root], bufs[r], byteCount, ncclUint8, root, n->comms[r], streams[r]->main));
             LCU_NCCL(n, n->GroupEnd());
+            g_last_broadcast_form = 1;
             return rebind_current();
         }
+        g_last_broadcast_form = 0;
         // Own path.  The buffer is cut into one shard per non-root device, each shard into pieces.
         //   pull lane of device g : loads piece after piece of shard g from the root (every byte leaves the root
         //                           exactly once; remote loads are the faster direction while the root only sends);

@@ -333,6 +333,9 @@ def _broadcast(ctxs, streams, G, n, use_nccl, root):
     bp = (C.c_void_p * G)(*[b.ptr for b in bufs])
     stp = (C.c_void_p * G)(*[s.handle for s in streams])
     api.check(lib.libreCuBroadcast(bp, root, n, G, stp, use_nccl))
+    ran = C.c_int(-9)
+    api.check(lib.libreCuBroadcastLastForm(C.byref(ran)))
+    assert ran.value == use_nccl, "the requested form did not run (a B200 group supports every form)"
     for s in streams:
         s.await_()
     for g in range(G):
@@ -365,6 +368,9 @@ def test_multicast_broadcast_large_misaligned_destinations_and_repeats(gpus):
         bp = (C.c_void_p * G)(*[b.ptr + (roff if g == root else offs[g]) for g, b in enumerate(bufs)])
         stp = (C.c_void_p * G)(*[s.handle for s in streams])
         api.check(lib.libreCuBroadcast(bp, root, n, G, stp, 3))
+        ran = C.c_int(-9)
+        api.check(lib.libreCuBroadcastLastForm(C.byref(ran)))
+        assert ran.value == (3 if roff % 16 == 0 else (0 if G == 2 else 2))   # misaligned root: the documented fall-back
         for s in streams:
             s.await_()
         for g in range(G):
