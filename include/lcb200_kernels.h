@@ -124,6 +124,17 @@ int lcb_alltoall_engines_step(int n_ranks, int rank, int step, int *dest, int *w
 int lcb_flag_post(void *flag, unsigned int value, lcbStream stream);
 int lcb_flag_wait(const void *flag, unsigned int value, unsigned int timeout_ms, lcbStream stream);
 
+/* One GPU's part of a ring broadcast root -> d1 -> d2 -> ..., fused into one kernel: for every chunk of
+ * chunk_bytes it waits until flags_in[chunk] has reached `epoch` (skipped on the root: flags_in NULL), copies
+ * the chunk from `local` into `next` with remote stores, and stores `epoch` into flags_next[chunk] (skipped on
+ * the last GPU: next NULL, which then only waits for its chunks).  The GPUs of a chain run one such kernel each
+ * at the same time; flags_* are arrays of one unsigned int per chunk in the memory of the GPU that waits on
+ * them, zero before the first use, epochs grow from call to call.  `bytes` and both buffers are multiples of
+ * 16; a wait is bounded by timeout_ms (1..10000: then bit 1 of the sticky error word, and the kernel returns).
+ * ctas = 0: two CTAs per SM.  ref: none (single-GPU reference, librecuda.cpp:61). */
+int lcb_bcast_ring_hop(const void *local, void *next, const void *flags_in, void *flags_next, size_t bytes, size_t chunk_bytes,
+                       unsigned int epoch, unsigned int timeout_ms, int ctas, lcbStream stream);
+
 /* Copies `bytes` bytes (a multiple of 16; both addresses 16-byte aligned) from ordinary device memory to a
  * MULTICAST address with multimem stores: NVSwitch writes the data into the memory of every GPU bound to the
  * multicast object at that offset, while it leaves the storing GPU only once.  mc_dst must be an address of a

@@ -235,8 +235,13 @@ LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAllEngines(void *const *peerRecvB
 // of devices and released by libreCuCtxDestroy of any of them, or at exit.
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, size_t chunkBytes, int nDev, const LibreCUstream *streams, int useNccl);
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount, int nDev, const LibreCUstream *streams, int useNccl);
-// The form the most recent libreCuBroadcast of this process actually ran (0..3; -1 before the first call): a
-// request for form 3 runs as 2 or 0 when multicast is not available or the root buffer is not 16-byte aligned.
+// useNccl == 4: a ring of kernels, one launch per GPU, each receiving its buffer from the previous GPU of the chain
+// root -> next device -> ... and forwarding it to the next in 64 KiB chunks as they arrive (remote stores, one flag
+// word per chunk in the receiver's memory, bounded waits): the forwarding is fused into the copy, so the pipeline
+// over the hops fills in tens of microseconds where the engine chain of form 2 needs whole pieces.  Buffers
+// must be 16-byte aligned (else form 2 runs).
+// The form the most recent libreCuBroadcast of this process actually ran (0..4; -1 before the first call): a
+// request for form 3 or 4 runs as 2 (0 with two GPUs) when its requirements are not met.
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuBroadcastLastForm(int *pFormOut);
 
 // Inter-process sharing of a libreCuMemAlloc allocation (one process per GPU).  `handle` points at

@@ -477,6 +477,39 @@ libreCudaStatus_t bcast_multicast(void *const *bufs, int root, size_t lo, size_t
 
 namespace {
 int g_last_broadcast_form = -1;  // the form the most recent libreCuBroadcast really ran (after any fall-back)
+
+// Per-device flag words of the ring broadcast (one per chunk), allocated on first use, grown on demand, kept
+// until the process exits (256 KiB per GPU for a 4 GiB broadcast in 64 KiB chunks).  They start at zero and
+// every call writes its own epoch, so they are never cleared.
+struct RingFlags {
+    unsigned int *ptr = nullptr;
+    size_t words = 0;
+};
+RingFlags g_ring_flags[64];
+unsigned int g_ring_epoch = 0;
+
+libreCudaStatus_t ring_flags_for(int device, size_t words, unsigned int **out) {
+    LIBRECUDA_VALIDATE(device >= 0 && device < 64, LIBRECUDA_ERROR_INVALID_DEVICE);
+    RingFlags &f = g_ring_flags[device];
+    if (f.words < words) {
+        LCU_CUDA(cudaSetDevice(device));
+        if (f.ptr != nullptr) {
+            LCU_CUDA(cudaDeviceSynchronize());
+            LCU_CUDA(cudaFree(f.ptr));
+            f.ptr = nullptr;
+            f.words = 0;
+        }
+        const size_t want = words < 65536 ? 65536 : words * 2;
+        LCU_CUDA(cudaMalloc(reinterpret_cast<void **>(&f.ptr), want * sizeof(unsigned int)));
+        LCU_CUDA(cudaMemset(f.ptr, 0, want * sizeof(unsigned int)));
+        LCU_CUDA(cudaDeviceSynchronize());
+        f.words = want;
+        // a fresh array is all zero: earlier epochs must not look "already delivered", and they do not, because
+        // every call uses a larger epoch than any before it
+    }
+    *out = f.ptr;
+    LIBRECUDA_SUCCEED();
+}
 }
 
 libreCudaStatus_t libreCuBroadcastLastForm(int *pFormOut) {
@@ -493,12 +526,47 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
         LIBRECUDA_ERR_PROPAGATE(check_group(nDev, streams, &devs));
         LIBRECUDA_VALIDATE(root >= 0 && root < nDev, LIBRECUDA_ERROR_INVALID_VALUE);
         for (int r = 0; r < nDev; ++r) LIBRECUDA_VALIDATE(bufs[r] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-        LIBRECUDA_VALIDATE(useNccl >= 0 && useNccl <= 3, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(useNccl >= 0 && useNccl <= 4, LIBRECUDA_ERROR_INVALID_VALUE);
         if (useNccl != 1) LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, bufs));
         for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(commence(streams[r]));
         if (byteCount == 0 || nDev == 1) LIBRECUDA_SUCCEED();
         std::vector<cudaStream_t> mains((size_t)nDev);
         for (int r = 0; r < nDev; ++r) mains[(size_t)r] = streams[r]->main;
+        if (useNccl == 4) {
+            // Ring of kernels: one launch per GPU that receives and forwards in 64 KiB chunks through flags in peer
+            // memory (ring_bcast_kernel).  All buffers must be 16-byte aligned; otherwise the engine chain runs.
+            bool aligned = true;
+            for (int r = 0; r < nDev; ++r) aligned = aligned && (reinterpret_cast<uintptr_t>(bufs[r]) & 15) == 0;
+            const size_t body = byteCount & ~(size_t)15;
+            if (aligned && body > 0) {
+                const int chunk_kib = lcb_tune_get("bcast_ring_chunk_kib") > 0 ? lcb_tune_get("bcast_ring_chunk_kib") : 64;
+                const size_t chunk = (size_t)chunk_kib << 10;
+                const size_t words = (body + chunk - 1) / chunk;
+                std::vector<unsigned int *> flags((size_t)nDev, nullptr);
+                for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(ring_flags_for(devs[(size_t)r], words, &flags[(size_t)r]));
+                LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));  // nobody may still be reading or writing the buffers
+                const unsigned int epoch = ++g_ring_epoch;
+                const int ctas = lcb_tune_get("bcast_ring_ctas");
+                for (int k = 0; k < nDev; ++k) {
+                    const int d = (root + k) % nDev, nx = (root + k + 1) % nDev;
+                    const bool last = k + 1 == nDev;
+                    LIBRECUDA_ERR_PROPAGATE(bind(streams[d]->ctx));
+                    LCU_LCB(lcb_bcast_ring_hop(bufs[d], last ? nullptr : bufs[nx], k == 0 ? nullptr : flags[(size_t)d],
+                                               last ? nullptr : flags[(size_t)nx], body, chunk, epoch, 2000, ctas, streams[d]->main));
+                }
+                if (body < byteCount) {  // the last few bytes: plain stores from the root into every buffer
+                    LIBRECUDA_ERR_PROPAGATE(bind(streams[root]->ctx));
+                    const uint8_t *src = static_cast<const uint8_t *>(bufs[root]);
+                    for (int g = 0; g < nDev; ++g)
+                        if (g != root)
+                            LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[g]) + body, src + body, byteCount - body, streams[root]->main));
+                }
+                LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+                g_last_broadcast_form = 4;
+                return rebind_current();
+            }
+            useNccl = nDev == 2 ? 0 : 2;
+        }
         if (useNccl == 3) {
             // Multicast (see bcast_multicast).  Needs multicast support on every GPU and a 16-byte aligned root
             // buffer; otherwise the call falls back to the copy-engine chain (form 2; form 0 with two GPUs).

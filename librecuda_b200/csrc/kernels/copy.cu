@@ -569,6 +569,85 @@ __device__ __forceinline__ void flag_wait(const unsigned int *flag, unsigned int
 }
 
 // ---------------------------------------------------------------------------------------------
+// ring broadcast: the copy fused with the forwarding
+// ---------------------------------------------------------------------------------------------
+// One kernel per GPU of a chain root -> d1 -> d2 -> ...  Every GPU but the last copies its own buffer, chunk by
+// chunk, into the NEXT GPU's buffer with remote stores; every GPU but the root first waits, per chunk, until the
+// previous GPU has delivered that chunk.  "Delivered" is a flag word per chunk in the receiving GPU's memory: the
+// sender stores the data, fences at system scope and stores the call's epoch into the flag with release
+// semantics; the receiver polls it with acquire loads (one thread per CTA, the others behind a barrier) and
+// reads the chunk with volatile loads.  Chunks are small (64 KiB), so a byte is forwarded a few microseconds
+// after it arrived and the pipeline over G - 1 hops fills in tens of microseconds -- the copy-engine chain
+// needs (G - 2) pieces of tens of MiB.  CTA b handles chunks b, b + grid, ...; all CTAs of a GPU work on one
+// compact window.  Waits are bounded: a CTA whose wait runs out raises kErrFlagTimeout, sets the GPU's abort
+// word so that the other CTAs stop at their next chunk, and returns.
+__device__ unsigned int g_ring_abort = 0;
+
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+template <bool ROOT>
+__global__ void __launch_bounds__(512) ring_bcast_kernel(const uint4 *__restrict__ local, uint4 *__restrict__ next,
+                                                         const unsigned int *flags_in, unsigned int *flags_next, size_t nvec,
+                                                         size_t chunk_vec, unsigned int epoch, unsigned long long timeout_ns) {
+    __shared__ int proceed;
+    const size_t nchunks = (nvec + chunk_vec - 1) / chunk_vec;
+    for (size_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        if (!ROOT) {
+            if (threadIdx.x == 0) {
+                int ok = 0;
+                unsigned long long t0, now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+                for (unsigned int polls = 0; polls < (1u << 26); ++polls) {
+                    unsigned int v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags_in + c) : "memory");
+                    if ((int)(v - epoch) >= 0) {
+                        ok = 1;
+                        break;
+                    }
+                    if (*(volatile unsigned int *)&g_ring_abort == epoch) break;  // another CTA of this GPU gave up
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                    if (now - t0 > timeout_ns) {
+                        raise_error(kErrFlagTimeout);
+                        *(volatile unsigned int *)&g_ring_abort = epoch;
+                        break;
+                    }
+                }
+                proceed = ok;
+            }
+            __syncthreads();
+            if (!proceed) return;
+        }
+        if (next != nullptr) {
+            const size_t first = c * chunk_vec;
+            const size_t end = first + chunk_vec < nvec ? first + chunk_vec : nvec;
+            constexpr int U = 4;
+            for (size_t base = first + threadIdx.x; base < end; base += (size_t)U * blockDim.x) {
+                uint4 v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const size_t j = base + (size_t)u * blockDim.x;
+                    if (j < end) v[u] = ROOT ? ld_stream<2>(local + j) : ld_volatile_v4(local + j);
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const size_t j = base + (size_t)u * blockDim.x;
+                    if (j < end) st_stream<1>(next + j, v[u]);
+                }
+            }
+            __threadfence_system();  // every thread's stores are performed system-wide before the barrier ...
+            __syncthreads();
+            if (threadIdx.x == 0)    // ... and the flag follows them
+                asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(flags_next + c), "r"(epoch) : "memory");
+        }
+        if (!ROOT) __syncthreads();  // `proceed` is rewritten in the next round
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 namespace {
@@ -972,6 +1051,32 @@ extern "C" int lcb_alltoall_push(void *const *peer_recv, const void *send, size_
 extern "C" int lcb_alltoall_pull(void *const *peer_send, void *recv, size_t chunk_bytes, int n_ranks, int rank,
                                  lcbStream stream) {
     return lcb::launch_alltoall(true, peer_send, recv, chunk_bytes, n_ranks, rank, stream);
+}
+
+extern "C" int lcb_bcast_ring_hop(const void *local, void *next, const void *flags_in, void *flags_next, size_t bytes,
+                                  size_t chunk_bytes, unsigned int epoch, unsigned int timeout_ms, int ctas, lcbStream stream) {
+    using namespace lcb;
+    if (bytes == 0) return 0;
+    if (local == nullptr || epoch == 0 || ctas < 0) return 1;
+    if (timeout_ms == 0 || timeout_ms > 10000u) return 1;
+    if (chunk_bytes < 4096 || (chunk_bytes & 15) || (bytes & 15)) return 1;
+    if ((reinterpret_cast<uintptr_t>(local) | reinterpret_cast<uintptr_t>(next)) & 15) return 1;
+    if ((reinterpret_cast<uintptr_t>(flags_in) | reinterpret_cast<uintptr_t>(flags_next)) & 3) return 1;
+    if (next != nullptr && flags_next == nullptr) return 1;
+    if (next == nullptr && flags_in == nullptr) return 0;  // neither receives nor forwards: nothing to do
+    const size_t nvec = bytes / 16, chunk_vec = chunk_bytes / 16;
+    const size_t nchunks = (nvec + chunk_vec - 1) / chunk_vec;
+    size_t grid = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * 2;
+    if (grid > nchunks) grid = nchunks;
+    NoPdlScope plain(true);  // a kernel that polls must not sit on the SMs before its predecessor on the stream is done
+    const unsigned long long timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint4 *l = static_cast<const uint4 *>(local);
+    uint4 *n = static_cast<uint4 *>(next);
+    const unsigned int *fi = static_cast<const unsigned int *>(flags_in);
+    unsigned int *fn = static_cast<unsigned int *>(flags_next);
+    if (flags_in == nullptr) return launch_kernel(ring_bcast_kernel<true>, (unsigned)grid, 512, 0, st, l, n, fi, fn, nvec, chunk_vec, epoch, timeout_ns);
+    return launch_kernel(ring_bcast_kernel<false>, (unsigned)grid, 512, 0, st, l, n, fi, fn, nvec, chunk_vec, epoch, timeout_ns);
 }
 
 extern "C" int lcb_flag_post(void *flag, unsigned int value, lcbStream stream) {

@@ -48,6 +48,8 @@ static const Tuning kDefaults = {
         /*phase_chunk*/ 32768,
         /*phase_stages*/ 6,
         /*phase_ns*/ 4000,
+        /*bcast_ring_chunk_kib*/ 64,
+        /*bcast_ring_ctas*/ 0,
         /*bcast_mc_piece_mib*/ 256,
         /*bcast_mc_slots*/ 2,
         /*bcast_mc_ctas*/ 64,
@@ -106,6 +108,8 @@ static bool knob_value_ok(const char *name, int v) {
     if (is("copy_vec_smem_pad") || is("tma_smem_pad") || is("memset_smem_pad")) return v >= 0 && v <= 200 * 1024;
     if (is("bcast_pull_ctas")) return v >= 0 && v <= 65536;
     if (is("bcast_mc_piece_mib")) return v >= 1 && v <= 1024;
+    if (is("bcast_ring_chunk_kib")) return v >= 4 && v <= 65536 && (v & (v - 1)) == 0;
+    if (is("bcast_ring_ctas")) return v >= 0 && v <= 4096;
     if (is("bcast_mc_slots")) return v >= 2 && v <= 16;
     return v >= 0;  // grid caps, thresholds and piece sizes: any non-negative value
 }
@@ -162,6 +166,8 @@ int check_launch() { return (int)cudaGetLastError(); }
     X(phase_chunk) \
     X(phase_stages) \
     X(phase_ns) \
+    X(bcast_ring_chunk_kib) \
+    X(bcast_ring_ctas) \
     X(bcast_mc_piece_mib) \
     X(bcast_mc_slots) \
     X(bcast_mc_ctas)

@@ -310,7 +310,7 @@ def test_lockstep_engine_all_to_all_recorded(gpus):
     ctxs[0].set_current()
 
 
-@pytest.mark.parametrize("use_nccl", [0, 1, 2, 3])
+@pytest.mark.parametrize("use_nccl", [0, 1, 2, 3, 4])
 @pytest.mark.parametrize("root", [0, 1])
 def test_broadcast(gpus, use_nccl, root):
     ctxs, streams = gpus
@@ -318,6 +318,7 @@ def test_broadcast(gpus, use_nccl, root):
     n = 37 * MiB + 1001
     api.tune(bcast_engine_piece_mib=4)     # form 2 with more than two GPUs: ten pieces, the last one ragged
     api.tune(bcast_mc_piece_mib=4, bcast_mc_slots=3)   # form 3: ten pieces through a ring of three slots, ragged end
+    api.tune(bcast_ring_chunk_kib=16, bcast_ring_ctas=37)   # form 4: 2369 chunks over 37 CTAs, the last chunk ragged
     try:
         _broadcast(ctxs, streams, G, n, use_nccl, root)
     finally:
