@@ -236,9 +236,9 @@ LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAllEngines(void *const *peerRecvB
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuAllToAll(void *const *recvBufs, void *const *sendBufs, size_t chunkBytes, int nDev, const LibreCUstream *streams, int useNccl);
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount, int nDev, const LibreCUstream *streams, int useNccl);
 // useNccl == 4: a ring of kernels, one launch per GPU, each receiving its buffer from the previous GPU of the chain
-// root -> next device -> ... and forwarding it to the next in 64 KiB chunks as they arrive (remote stores, one flag
-// word per chunk in the receiver's memory, bounded waits): the forwarding is fused into the copy, so the pipeline
-// over the hops fills in tens of microseconds where the engine chain of form 2 needs whole pieces.  Buffers
+// root -> next device -> ... and forwarding it to the next in 128 KiB chunks as they arrive (remote stores, one flag
+// word per chunk in the receiver's memory, bounded waits): the forwarding is fused into the copy, so a hop adds
+// tens of microseconds where the engine chain of form 2 adds the time of a whole piece (676-679 GB/s at 4 GPUs).  Buffers
 // must be 16-byte aligned (else form 2 runs).
 // The form the most recent libreCuBroadcast of this process actually ran (0..4; -1 before the first call): a
 // request for form 3 or 4 runs as 2 (0 with two GPUs) when its requirements are not met.

@@ -479,7 +479,7 @@ namespace {
 int g_last_broadcast_form = -1;  // the form the most recent libreCuBroadcast really ran (after any fall-back)
 
 // Per-device flag words of the ring broadcast (one per chunk), allocated on first use, grown on demand, kept
-// until the process exits (256 KiB per GPU for a 4 GiB broadcast in 64 KiB chunks).  They start at zero and
+// until the process exits (128 KiB per GPU for a 4 GiB broadcast in 128 KiB chunks).  They start at zero and
 // every call writes its own epoch, so they are never cleared.
 struct RingFlags {
     unsigned int *ptr = nullptr;
@@ -533,13 +533,16 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
         std::vector<cudaStream_t> mains((size_t)nDev);
         for (int r = 0; r < nDev; ++r) mains[(size_t)r] = streams[r]->main;
         if (useNccl == 4) {
-            // Ring of kernels: one launch per GPU that receives and forwards in 64 KiB chunks through flags in peer
+            // Ring of kernels: one launch per GPU that receives and forwards in 128 KiB chunks through flags in peer
             // memory (ring_bcast_kernel).  All buffers must be 16-byte aligned; otherwise the engine chain runs.
+            // Measured at 4 GPUs, 4 GiB: 676-679 GB/s with 128 KiB x 296 CTAs or 256 KiB x 148 (590 with 64 KiB x 296,
+            // 369 with 32 KiB: the per-chunk wait, fence and flag cost a few microseconds), against 689 for the engine
+            // chain and 669-674 for NCCL there.
             bool aligned = true;
             for (int r = 0; r < nDev; ++r) aligned = aligned && (reinterpret_cast<uintptr_t>(bufs[r]) & 15) == 0;
             const size_t body = byteCount & ~(size_t)15;
             if (aligned && body > 0) {
-                const int chunk_kib = lcb_tune_get("bcast_ring_chunk_kib") > 0 ? lcb_tune_get("bcast_ring_chunk_kib") : 64;
+                const int chunk_kib = lcb_tune_get("bcast_ring_chunk_kib") > 0 ? lcb_tune_get("bcast_ring_chunk_kib") : 128;
                 const size_t chunk = (size_t)chunk_kib << 10;
                 const size_t words = (body + chunk - 1) / chunk;
                 std::vector<unsigned int *> flags((size_t)nDev, nullptr);

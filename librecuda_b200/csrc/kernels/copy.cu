@@ -576,9 +576,9 @@ __device__ __forceinline__ void flag_wait(const unsigned int *flag, unsigned int
 // previous GPU has delivered that chunk.  "Delivered" is a flag word per chunk in the receiving GPU's memory: the
 // sender stores the data, fences at system scope and stores the call's epoch into the flag with release
 // semantics; the receiver polls it with acquire loads (one thread per CTA, the others behind a barrier) and
-// reads the chunk with volatile loads.  Chunks are small (64 KiB), so a byte is forwarded a few microseconds
-// after it arrived and the pipeline over G - 1 hops fills in tens of microseconds -- the copy-engine chain
-// needs (G - 2) pieces of tens of MiB.  CTA b handles chunks b, b + grid, ...; all CTAs of a GPU work on one
+// reads the chunk with volatile loads.  Chunks are small (128 KiB by default), so a byte is forwarded some tens
+// of microseconds after it arrived -- all CTAs' chunks in flight, about 37 MiB, divided by the link rate -- where
+// the copy-engine chain forwards whole pieces of tens of MiB.  CTA b handles chunks b, b + grid, ...; all CTAs of a GPU work on one
 // compact window.  Waits are bounded: a CTA whose wait runs out raises kErrFlagTimeout, sets the GPU's abort
 // word so that the other CTAs stop at their next chunk, and returns.
 __device__ unsigned int g_ring_abort = 0;
@@ -638,10 +638,11 @@ __global__ void __launch_bounds__(512) ring_bcast_kernel(const uint4 *__restrict
                     if (j < end) st_stream<1>(next + j, v[u]);
                 }
             }
-            __threadfence_system();  // every thread's stores are performed system-wide before the barrier ...
-            __syncthreads();
-            if (threadIdx.x == 0)    // ... and the flag follows them
-                asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(flags_next + c), "r"(epoch) : "memory");
+            __syncthreads();  // every thread's stores are ordered before thread 0's fence by the barrier ...
+            if (threadIdx.x == 0) {
+                __threadfence_system();  // ... the fence makes them visible system-wide (it is cumulative) ...
+                asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(flags_next + c), "r"(epoch) : "memory");  // ... before the flag
+            }
         }
         if (!ROOT) __syncthreads();  // `proceed` is rewritten in the next round
     }

@@ -48,7 +48,7 @@ static const Tuning kDefaults = {
         /*phase_chunk*/ 32768,
         /*phase_stages*/ 6,
         /*phase_ns*/ 4000,
-        /*bcast_ring_chunk_kib*/ 64,
+        /*bcast_ring_chunk_kib*/ 128,
         /*bcast_ring_ctas*/ 0,
         /*bcast_mc_piece_mib*/ 256,
         /*bcast_mc_slots*/ 2,
