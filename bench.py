@@ -238,6 +238,11 @@ def run_ours(args):
     multi = world > 1
     dist = None
     torch = None
+    # Libraries underneath (NCCL prints its version line) write to file descriptor 1; the contract is ONE line on
+    # stdout, so everything but the final JSON line is sent to stderr.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     if multi:
         import torch
         import torch.distributed as dist
@@ -439,7 +444,9 @@ def run_ours(args):
         }
         if nvlink is not None:
             line["nvlink"] = nvlink
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        print(json.dumps(line), flush=True)
     return 0 if verified else 1
 
 
