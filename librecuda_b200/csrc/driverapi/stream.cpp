@@ -274,6 +274,12 @@ libreCudaStatus_t libreCuStreamCreate(LibreCUstream *pStreamOut, uint32_t flags)
         st->ctx = ctx;
         LCU_CUDA(cudaStreamCreateWithFlags(&st->main, cudaStreamNonBlocking));
         LCU_CUDA(cudaEventCreateWithFlags(&st->fork, cudaEventDisableTiming));
+        // The side lanes of async operations are made here, not at their first use: creating a CUDA stream while
+        // kernels are running can wait for them, which cost the first burst of async launches most of its overlap.
+        for (int i = 0; i < kSideLanes; ++i) {
+            LCU_CUDA(cudaStreamCreateWithFlags(&st->side[i], cudaStreamNonBlocking));
+            LCU_CUDA(cudaEventCreateWithFlags(&st->side_done[i], cudaEventDisableTiming));
+        }
         *pStreamOut = st.release();
         LIBRECUDA_SUCCEED();
     });
