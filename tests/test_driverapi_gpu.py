@@ -338,7 +338,7 @@ def test_await_reports_a_kernel_that_gave_up_a_bounded_wait(stream):
 
 def test_host_wait_deadline_from_the_environment():
     # LIBRECUDA_WAIT_TIMEOUT_MS is read once per process, so the case runs in a child: a kernel that spins for
-    # 0.4 s (bounded by its cycle count, nothing hangs), a 50 ms limit -> Await and EventSynchronize give up with
+    # a quarter of a second (bounded by its cycle count, nothing hangs), a 50 ms limit -> Await and EventSynchronize give up with
     # NOT_READY while it runs, and succeed when repeated after it has finished
     import os
     import subprocess
@@ -357,7 +357,7 @@ st = api.Stream()
 out = api.DeviceBuffer(4, map_to_cpu=True)
 C.c_float.from_address(out.ptr).value = 0.0
 ev = api.Event()
-st.launch(fn, (1, 1, 1), (1, 1, 1), 0, [C.c_void_p(out.ptr), C.c_longlong(int(0.4 * 1.9e9))])
+st.launch(fn, (1, 1, 1), (1, 1, 1), 0, [C.c_void_p(out.ptr), C.c_longlong(int(0.25 * 1.9e9))])
 ev.record(st)
 st.commence()
 t0 = time.perf_counter()
