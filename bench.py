@@ -38,9 +38,10 @@ UNIT = "GB/s"
 NVLINK_NOMINAL = 900.0   # GB/s per direction per GPU
 SRC_STABLE = 0x100       # LCB_COPY_SRC_STABLE: nothing in flight on the stream writes the copy's source
 # dram__bytes_read.sum + dram__bytes_write.sum of the very launch the bench times (1 GiB, AUTO | SRC_STABLE ->
-# copy_tma_kernel<2,1,0>) from an ncu capture of `bench.py --case copy_auto_stable --bytes 1073741824`: reads
-# 1.0738 GB (the source), writes 1.0229 GB (the destination less ~51 MB still dirty in L2 at kernel exit)
-NCU_TRAFFIC_1GIB = 2_096_700_000
+# copy_tma_kernel<3,2,0>, 12 KiB per CTA) from an ncu capture of `bench.py --case copy_auto_stable --bytes
+# 1073741824`: reads 1.0738 GB (the source), writes 1.0244 GB (the destination less ~50 MB still dirty in L2 at
+# kernel exit)
+NCU_TRAFFIC_1GIB = 2_098_200_000
 
 
 def measured_hbm_peak():
@@ -312,7 +313,7 @@ def run_ours(args):
                 "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
                 "frac_of_nominal_8000": round(achieved / 8000.0, 4), "traffic": NCU_TRAFFIC_1GIB,
                 "traffic_note": "dram read+write bytes of this 1 GiB launch under ncu (reads = source size, writes = "
-                                "destination size minus ~51 MB left dirty in L2 at kernel exit)"}
+                                "destination size minus ~50 MB left dirty in L2 at kernel exit)"}
 
     def frac_entry(nbytes_moved, t_ms, extra=None):
         gbps = nbytes_moved / (t_ms * 1e-3) / 1e9

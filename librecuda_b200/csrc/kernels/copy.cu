@@ -804,19 +804,14 @@ int launch_tma(const Split &sp, int ctas, cudaStream_t st, int early, Plan *plan
     uint32_t chunk = (uint32_t)tu.tma_chunk;
     int S = tu.tma_stages, L = tu.tma_lookahead;
     if (chunk == 0) {
-        // chosen by size (every CTA moves ONE chunk; measured on B200 with the loads issued ahead of the stream
-        // wait): below 512 MiB an 8 KiB chunk with three stages' worth of shared memory reserved, which caps
-        // residency at 9 CTAs per SM (6.86 / 6.96 TB/s at 128 / 256 MiB against 6.85 / 6.95 for one 32 KiB
-        // chunk and 6.67 / 6.81 for the vector kernel); from 512 MiB up a 32 KiB chunk (6.97-6.98 TB/s)
-        if (body < ((size_t)512 << 20)) {
-            chunk = 8192;
-            S = 3;
-            L = 2;
-        } else {
-            chunk = 32768;
-            S = 2;
-            L = 1;
-        }
+        // One shape for every size (every CTA moves ONE chunk; measured on B200 with the loads issued ahead of the
+        // stream wait): a 12 KiB chunk with three stages' worth of shared memory reserved, which caps residency at
+        // 6 CTAs per SM.  It is first or second of 50 (chunk, reservation) pairs at 128 MiB, 256 MiB, 512 MiB and
+        // 1 GiB (6880 / 6995 / 6987 / 6997 GB/s; 8 KiB x 3: 6862 / 6967 / 6944 / 6967; 32 KiB x 2: 6882 / 6977 /
+        // 6961 / 6977; the vector kernel 6766-6820 / 6858-6885 / 6913-6921 / 6949-6951).
+        chunk = 12288;
+        S = 3;
+        L = 2;
     }
     if (chunk < 1024 || chunk > 65536 || (chunk & 127)) return 1;
     const size_t smem = (size_t)S * chunk + 8 * S;

@@ -162,8 +162,8 @@ def test_copy_plan_query_follows_the_dispatcher():
     MiB = 1 << 20
     assert plan(4096, 1 << 40, 4096).startswith("copy_vec_kernel<-1,1,")              # small path
     assert plan(4096, 1 << 40, 32 * MiB).startswith("copy_vec_kernel<-1,")           # vector kernel below 96 MiB
-    assert plan(4096, 1 << 40, 256 * MiB).startswith("copy_tma_kernel<3,2,0>, 32768 CTAs")   # 8 KiB chunks
-    assert plan(4096, 1 << 40, 1 << 30).startswith("copy_tma_kernel<2,1,0>, 32768 CTAs")     # 32 KiB chunks
+    assert plan(4096, 1 << 40, 256 * MiB).startswith("copy_tma_kernel<3,2,0>, 21846 CTAs")   # 12 KiB chunks
+    assert plan(4096, 1 << 40, 1 << 30).startswith("copy_tma_kernel<3,2,0>, 87382 CTAs")     # the same shape at every size
     assert plan(4096, (1 << 40) + 1, 1 << 30).startswith("copy_vec_kernel<0,4,2>, 32768 CTAs x 512")  # realign by 1 byte
     assert plan(4096, (1 << 40) + 13, 1 << 30).startswith("copy_vec_kernel<3,4,2>")
     assert "loads before the stream wait" in plan(4096, 1 << 40, 1 << 30, 0x100)
