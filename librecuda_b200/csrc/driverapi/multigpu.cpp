@@ -533,23 +533,33 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
         std::vector<cudaStream_t> mains((size_t)nDev);
         for (int r = 0; r < nDev; ++r) mains[(size_t)r] = streams[r]->main;
         if (useNccl == 4) {
-            // Ring of kernels: one launch per GPU that receives and forwards in 128 KiB chunks through flags in peer
-            // memory (ring_bcast_kernel).  All buffers must be 16-byte aligned; otherwise the engine chain runs.
-            // Measured at 4 GPUs, 4 GiB: 676-679 GB/s with 128 KiB x 296 CTAs or 256 KiB x 148 (590 with 64 KiB x 296,
-            // 369 with 32 KiB: the per-chunk wait, fence and flag cost a few microseconds), against 689 for the engine
-            // chain and 669-674 for NCCL there.
+            // Ring of kernels: one launch per GPU that receives and forwards in small chunks through flags in peer
+            // memory.  All buffers must be 16-byte aligned; otherwise the engine chain runs.  Two kernels:
+            //   one chunk per warp (ring_bcast_warp_kernel, the default): 16 KiB chunks; 148 CTAs up to 4 GPUs, 111
+            //     beyond.  Measured, 4 GiB: 687 GB/s at 4 GPUs (NCCL 670, engine chain 689), 669-674 at 8 (NCCL 665).
+            //     Time = bytes / 705 GB/s + 0.15 ms at 4 GPUs, + 0.30 ms at 8: every hop adds about the time the chunks
+            //     of all resident warps take to drain (28-37 MiB), which is why fewer CTAs win on the longer chain.
+            //   one chunk per CTA (ring_bcast_kernel, tunable bcast_ring_warp = 0): 128 KiB chunks x 296 CTAs, 676 at 4
+            //     GPUs and 654 at 8 (+ 0.22 / 0.47 ms); 590 with 64 KiB, 369 with 32 KiB chunks, because the whole CTA
+            //     idles while one thread's release waits for the remote stores to be acknowledged.
             bool aligned = true;
             for (int r = 0; r < nDev; ++r) aligned = aligned && (reinterpret_cast<uintptr_t>(bufs[r]) & 15) == 0;
             const size_t body = byteCount & ~(size_t)15;
             if (aligned && body > 0) {
-                const int chunk_kib = lcb_tune_get("bcast_ring_chunk_kib") > 0 ? lcb_tune_get("bcast_ring_chunk_kib") : 128;
+                const bool per_warp = lcb_tune_get("bcast_ring_warp") != 0;
+                const int chunk_kib = lcb_tune_get("bcast_ring_chunk_kib") > 0 ? lcb_tune_get("bcast_ring_chunk_kib") : (per_warp ? 16 : 128);
                 const size_t chunk = (size_t)chunk_kib << 10;
                 const size_t words = (body + chunk - 1) / chunk;
                 std::vector<unsigned int *> flags((size_t)nDev, nullptr);
                 for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(ring_flags_for(devs[(size_t)r], words, &flags[(size_t)r]));
                 LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));  // nobody may still be reading or writing the buffers
                 const unsigned int epoch = ++g_ring_epoch;
-                const int ctas = lcb_tune_get("bcast_ring_ctas");
+                int ctas = lcb_tune_get("bcast_ring_ctas");
+                if (ctas <= 0 && per_warp) {  // per SM: one CTA up to 4 GPUs, three quarters of one beyond
+                    int sms = 0;
+                    LCU_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, devs[(size_t)root]));
+                    ctas = nDev <= 4 ? sms : (sms * 3) / 4;
+                }
                 for (int k = 0; k < nDev; ++k) {
                     const int d = (root + k) % nDev, nx = (root + k + 1) % nDev;
                     const bool last = k + 1 == nDev;

@@ -648,6 +648,66 @@ __global__ void __launch_bounds__(512) ring_bcast_kernel(const uint4 *__restrict
     }
 }
 
+// The same protocol with one chunk per WARP (a few KiB, one flag word each): a warp polls, loads, stores, posts and
+// moves on by itself, so nothing in the CTA idles while one warp's release waits for its remote stores to be
+// acknowledged, and a byte can be forwarded a few microseconds after it arrived instead of after the time all
+// CTAs' chunks take to drain.  Every lane polls the flag (one request per warp: same address) and so holds its
+// own acquire; the release is lane 0's, after a warp barrier, and is cumulative over what the barrier ordered
+// before it.  Warp w of the grid handles chunks w, w + W, ...
+template <bool ROOT>
+__global__ void __launch_bounds__(512) ring_bcast_warp_kernel(const uint4 *__restrict__ local, uint4 *__restrict__ next,
+                                                              const unsigned int *flags_in, unsigned int *flags_next, size_t nvec,
+                                                              size_t chunk_vec, unsigned int epoch, unsigned long long timeout_ns) {
+    const unsigned lane = threadIdx.x & 31u;
+    const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+    const size_t nchunks = (nvec + chunk_vec - 1) / chunk_vec;
+    for (size_t c = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); c < nchunks; c += warps) {
+        if (!ROOT) {
+            bool ok = false;
+            unsigned long long t0, now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+            for (unsigned int polls = 0; polls < (1u << 26); ++polls) {  // uniform over the warp: same address, same clock
+                unsigned int v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags_in + c) : "memory");
+                if ((int)(v - epoch) >= 0) {
+                    ok = true;
+                    break;
+                }
+                if (*(volatile unsigned int *)&g_ring_abort == epoch) break;  // another warp of this GPU gave up
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (now - t0 > timeout_ns) {
+                    if (lane == 0) {
+                        raise_error(kErrFlagTimeout);
+                        *(volatile unsigned int *)&g_ring_abort = epoch;
+                    }
+                    break;
+                }
+            }
+            if (!__all_sync(0xffffffffu, ok)) return;
+        }
+        if (next != nullptr) {
+            const size_t first = c * chunk_vec;
+            const size_t end = first + chunk_vec < nvec ? first + chunk_vec : nvec;
+            constexpr int U = 8;
+            for (size_t base = first + lane; base < end; base += (size_t)U * 32) {
+                uint4 v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const size_t j = base + (size_t)u * 32;
+                    if (j < end) v[u] = ROOT ? ld_stream<2>(local + j) : ld_volatile_v4(local + j);
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const size_t j = base + (size_t)u * 32;
+                    if (j < end) st_stream<1>(next + j, v[u]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(flags_next + c), "r"(epoch) : "memory");
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
@@ -946,6 +1006,11 @@ int preload_copy_kernels() {
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_vec_kernel<3, 4, 2>);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_tma_kernel<2, 1, false>);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, copy_tma_kernel<3, 2, false>);
+    // kernels that wait for another GPU's kernel must not meet a module load at their first launch
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ring_bcast_kernel<true>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ring_bcast_kernel<false>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ring_bcast_warp_kernel<true>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ring_bcast_warp_kernel<false>);
     return (int)e;
 }
 }  // namespace lcb
@@ -1071,6 +1136,11 @@ extern "C" int lcb_bcast_ring_hop(const void *local, void *next, const void *fla
     uint4 *n = static_cast<uint4 *>(next);
     const unsigned int *fi = static_cast<const unsigned int *>(flags_in);
     unsigned int *fn = static_cast<unsigned int *>(flags_next);
+    if (tuning().bcast_ring_warp) {  // one chunk per warp: 16 warps per CTA share the chunks
+        if (grid * 16 > nchunks) grid = (nchunks + 15) / 16;
+        if (flags_in == nullptr) return launch_kernel(ring_bcast_warp_kernel<true>, (unsigned)grid, 512, 0, st, l, n, fi, fn, nvec, chunk_vec, epoch, timeout_ns);
+        return launch_kernel(ring_bcast_warp_kernel<false>, (unsigned)grid, 512, 0, st, l, n, fi, fn, nvec, chunk_vec, epoch, timeout_ns);
+    }
     if (flags_in == nullptr) return launch_kernel(ring_bcast_kernel<true>, (unsigned)grid, 512, 0, st, l, n, fi, fn, nvec, chunk_vec, epoch, timeout_ns);
     return launch_kernel(ring_bcast_kernel<false>, (unsigned)grid, 512, 0, st, l, n, fi, fn, nvec, chunk_vec, epoch, timeout_ns);
 }

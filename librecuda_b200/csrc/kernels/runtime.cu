@@ -48,11 +48,12 @@ static const Tuning kDefaults = {
         /*phase_chunk*/ 32768,
         /*phase_stages*/ 6,
         /*phase_ns*/ 4000,
-        /*bcast_ring_chunk_kib*/ 128,
+        /*bcast_ring_chunk_kib*/ 0,
         /*bcast_ring_ctas*/ 0,
         /*bcast_mc_piece_mib*/ 256,
         /*bcast_mc_slots*/ 2,
         /*bcast_mc_ctas*/ 64,
+        /*bcast_ring_warp*/ 1,
 };
 
 static void apply_env_overrides() {  // LCB_TUNE="knob=value,knob=value": overrides for experiments
@@ -103,12 +104,12 @@ static bool knob_value_ok(const char *name, int v) {
     if (is("memset_path")) return v >= 0 && v <= 2;
     if (is("memset_issuers")) return v >= 1 && v <= 8;
     if (is("memset_bulk_ctas_sm")) return v >= 1 && v <= 32;
-    if (is("tma_cache_hint") || is("memset_cache_hint") || is("pdl")) return v == 0 || v == 1;
+    if (is("tma_cache_hint") || is("memset_cache_hint") || is("pdl") || is("bcast_ring_warp")) return v == 0 || v == 1;
     if (is("auto_tma_min_mib")) return v >= -1;
     if (is("copy_vec_smem_pad") || is("tma_smem_pad") || is("memset_smem_pad")) return v >= 0 && v <= 200 * 1024;
     if (is("bcast_pull_ctas")) return v >= 0 && v <= 65536;
     if (is("bcast_mc_piece_mib")) return v >= 1 && v <= 1024;
-    if (is("bcast_ring_chunk_kib")) return v >= 4 && v <= 65536 && (v & (v - 1)) == 0;
+    if (is("bcast_ring_chunk_kib")) return v == 0 || (v >= 4 && v <= 65536 && (v & (v - 1)) == 0);
     if (is("bcast_ring_ctas")) return v >= 0 && v <= 4096;
     if (is("bcast_mc_slots")) return v >= 2 && v <= 16;
     return v >= 0;  // grid caps, thresholds and piece sizes: any non-negative value
@@ -170,7 +171,8 @@ int check_launch() { return (int)cudaGetLastError(); }
     X(bcast_ring_ctas) \
     X(bcast_mc_piece_mib) \
     X(bcast_mc_slots) \
-    X(bcast_mc_ctas)
+    X(bcast_mc_ctas) \
+    X(bcast_ring_warp)
 
 extern "C" int lcb_tune(const char *name, int value) {
     using lcb::tuning;

@@ -325,6 +325,25 @@ def test_broadcast(gpus, use_nccl, root):
         api.tune_reset()
 
 
+@pytest.mark.parametrize("per_warp,chunk_kib,ctas", [(1, 8, 5), (1, 0, 0), (0, 16, 37), (0, 0, 0)])
+def test_ring_broadcast_chunk_per_warp_and_per_cta(gpus, per_warp, chunk_kib, ctas):
+    # Form 4 with either kernel: a chunk (and its flag) per warp or per CTA, with few workers and small chunks
+    # (every worker takes many turns, the last chunk ragged) and with the shapes the library picks; the last GPU
+    # of the chain as root, twice in a row (the second call waits on the next epoch of the same flag words).
+    ctxs, streams = gpus
+    G = len(ctxs)
+    api.tune(bcast_ring_warp=per_warp, bcast_ring_chunk_kib=chunk_kib, bcast_ring_ctas=ctas)
+    try:
+        _broadcast(ctxs, streams, G, 37 * MiB + 1001, 4, G - 1)
+        _broadcast(ctxs, streams, G, 37 * MiB + 1001, 4, G - 1)
+    finally:
+        api.tune_reset()
+    for g in range(G):
+        ctxs[g].set_current()
+        assert api.device_error_word() == 0
+    ctxs[0].set_current()
+
+
 def _broadcast(ctxs, streams, G, n, use_nccl, root):
     data = oracle.random_bytes(n, seed=3)
     bufs = [_alloc_on(ctxs[g], n) for g in range(G)]
