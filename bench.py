@@ -1001,7 +1001,7 @@ def run_one_process(api, ctx0, G, reps):
     api.lcb_check(lib.lcb_fill_splitmix64(bufs[0].ptr, bsz, 3, natives[0]), "fill")
     streams[0].run()
     bp = arr([b.ptr for b in bufs])
-    forms = [(4, "libreCuBroadcast_4_ring_of_kernels"), (3, "libreCuBroadcast_3_multicast_stores"), (0, "libreCuBroadcast_0_pull_and_forward_kernels"),
+    forms = [(5, "libreCuBroadcast_5_two_trees_of_kernels"), (4, "libreCuBroadcast_4_ring_of_kernels"), (3, "libreCuBroadcast_3_multicast_stores"), (0, "libreCuBroadcast_0_pull_and_forward_kernels"),
              (2, "libreCuBroadcast_2_copy_engine_chain"), (1, "libreCuBroadcast_1_nccl")]
     for form, name in forms:
         for g in range(1, G):

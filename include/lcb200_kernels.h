@@ -137,6 +137,24 @@ int lcb_flag_wait(const void *flag, unsigned int value, unsigned int timeout_ms,
 int lcb_bcast_ring_hop(const void *local, void *next, const void *flags_in, void *flags_next, size_t bytes, size_t chunk_bytes,
                        unsigned int epoch, unsigned int timeout_ms, int ctas, lcbStream stream);
 
+/* Broadcast down two complementary binary trees, one per half of the buffer, instead of one chain: the depth is
+ * 1 + log2(n_ranks - 1) hops instead of n_ranks - 1, every GPU still receives each byte once and sends at most one
+ * buffer's worth.  lcb_bcast_tree_plan is the topology as a pure function (no GPU): for `rank` it gives
+ * parents[0..1] (the rank it receives the first / second half from; -1 on the root) and children[0..3]
+ * (children[0..1]: where it forwards the first half, children[2..3]: the second; -1 = none).  The non-root ranks
+ * in the order root+1, root+2, ... form a heap for the first half and the same heap in reverse order for the
+ * second, so a rank with children in one tree has none in the other.
+ * lcb_bcast_tree_node is one GPU's kernel: for every chunk of chunk_bytes (one warp each, as in the ring's
+ * chunk-per-warp form) it waits for flags_in[chunk] (skipped on the root: flags_in NULL), stores the chunk into
+ * the children's buffers and posts children_flags[k][chunk].  children / children_flags are arrays of four
+ * pointers laid out like the plan's children (NULL = none; whole buffers and whole flag arrays, indexed like
+ * `local` and flags_in); chunks below split_chunk belong to the first half.  Alignment, epochs, timeout and the
+ * error word are those of lcb_bcast_ring_hop.  ctas = 0: one CTA per SM.  ref: none (single-GPU reference). */
+int lcb_bcast_tree_plan(int n_ranks, int root, int rank, int *parents, int *children);
+int lcb_bcast_tree_node(const void *local, const void *flags_in, void *const *children, void *const *children_flags,
+                        size_t bytes, size_t chunk_bytes, size_t split_chunk, unsigned int epoch, unsigned int timeout_ms,
+                        int ctas, lcbStream stream);
+
 /* Copies `bytes` bytes (a multiple of 16; both addresses 16-byte aligned) from ordinary device memory to a
  * MULTICAST address with multimem stores: NVSwitch writes the data into the memory of every GPU bound to the
  * multicast object at that offset, while it leaves the storing GPU only once.  mc_dst must be an address of a

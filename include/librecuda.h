@@ -240,8 +240,12 @@ LIBRECUDA_EXPORT libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root,
 // word per chunk in the receiver's memory, bounded waits): the forwarding is fused into the copy, so a hop adds
 // tens of microseconds where the engine chain of form 2 adds the time of a whole piece (676-679 GB/s at 4 GPUs).  Buffers
 // must be 16-byte aligned (else form 2 runs).
-// The form the most recent libreCuBroadcast of this process actually ran (0..4; -1 before the first call): a
-// request for form 3 or 4 runs as 2 (0 with two GPUs) when its requirements are not met.
+// useNccl == 5: the same fused kernels over two complementary binary trees instead of one chain: the first half of the
+// buffer goes down a tree over the non-root GPUs, the second half down a tree in which the inner nodes of the first
+// are leaves, so the last GPU is 1 + log2(nDev - 1) hops from the root instead of nDev - 1 while every GPU still
+// receives each byte once and sends at most one buffer's worth.  Same alignment rule and fall-back as form 4.
+// The form the most recent libreCuBroadcast of this process actually ran (0..5; -1 before the first call): a
+// request for form 3, 4 or 5 runs as 2 (0 with two GPUs) when its requirements are not met.
 LIBRECUDA_EXPORT libreCudaStatus_t libreCuBroadcastLastForm(int *pFormOut);
 
 // Inter-process sharing of a libreCuMemAlloc allocation (one process per GPU).  `handle` points at

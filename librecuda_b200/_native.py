@@ -39,6 +39,8 @@ LCB_FUNCTIONS = {
     "lcb_alltoall_engines": (i32, [vpp, vp, sz, i32, i32, vp, vpp, C.c_uint, C.c_uint, vp, vp]),
     "lcb_alltoall_engines_step": (i32, [i32, i32, i32] + [C.POINTER(i32)] * 5),
     "lcb_bcast_ring_hop": (i32, [vp, vp, vp, vp, sz, sz, C.c_uint, C.c_uint, i32, vp]),
+    "lcb_bcast_tree_plan": (i32, [i32, i32, i32, C.POINTER(i32), C.POINTER(i32)]),
+    "lcb_bcast_tree_node": (i32, [vp, vp, vpp, vpp, sz, sz, sz, C.c_uint, C.c_uint, i32, vp]),
     "lcb_flag_post": (i32, [vp, C.c_uint, vp]),
     "lcb_flag_wait": (i32, [vp, C.c_uint, C.c_uint, vp]),
     "lcb_fill_splitmix64": (i32, [vp, sz, u64, vp]),

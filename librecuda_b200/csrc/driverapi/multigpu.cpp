@@ -526,12 +526,53 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
         LIBRECUDA_ERR_PROPAGATE(check_group(nDev, streams, &devs));
         LIBRECUDA_VALIDATE(root >= 0 && root < nDev, LIBRECUDA_ERROR_INVALID_VALUE);
         for (int r = 0; r < nDev; ++r) LIBRECUDA_VALIDATE(bufs[r] != nullptr, LIBRECUDA_ERROR_INVALID_VALUE);
-        LIBRECUDA_VALIDATE(useNccl >= 0 && useNccl <= 4, LIBRECUDA_ERROR_INVALID_VALUE);
+        LIBRECUDA_VALIDATE(useNccl >= 0 && useNccl <= 5, LIBRECUDA_ERROR_INVALID_VALUE);
         if (useNccl != 1) LIBRECUDA_ERR_PROPAGATE(check_reachable(nDev, streams, bufs));
         for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(commence(streams[r]));
         if (byteCount == 0 || nDev == 1) LIBRECUDA_SUCCEED();
         std::vector<cudaStream_t> mains((size_t)nDev);
         for (int r = 0; r < nDev; ++r) mains[(size_t)r] = streams[r]->main;
+        if (useNccl == 5) {
+            // Two complementary binary trees of fused kernels (tree_bcast_kernel, lcb_bcast_tree_plan): half of the
+            // chunks per tree, one launch per GPU.  Same requirements and fall-back as the ring.
+            bool aligned = true;
+            for (int r = 0; r < nDev; ++r) aligned = aligned && (reinterpret_cast<uintptr_t>(bufs[r]) & 15) == 0;
+            const size_t body = byteCount & ~(size_t)15;
+            if (aligned && body > 0) {
+                const int chunk_kib = lcb_tune_get("bcast_ring_chunk_kib") > 0 ? lcb_tune_get("bcast_ring_chunk_kib") : 16;
+                const size_t chunk = (size_t)chunk_kib << 10;
+                const size_t words = (body + chunk - 1) / chunk;
+                std::vector<unsigned int *> flags((size_t)nDev, nullptr);
+                for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(ring_flags_for(devs[(size_t)r], words, &flags[(size_t)r]));
+                LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));  // nobody may still be reading or writing the buffers
+                const unsigned int epoch = ++g_ring_epoch;
+                const int ctas = lcb_tune_get("bcast_ring_ctas");
+                for (int k = 0; k < nDev; ++k) {  // the root first, then in chain order: parents come before children
+                    const int d = (root + k) % nDev;
+                    int parents[2], kids[4];
+                    LIBRECUDA_VALIDATE(lcb_bcast_tree_plan(nDev, root, d, parents, kids) == 0, LIBRECUDA_ERROR_UNKNOWN);
+                    void *kid_bufs[4], *kid_flags[4];
+                    for (int c = 0; c < 4; ++c) {
+                        kid_bufs[c] = kids[c] < 0 ? nullptr : bufs[kids[c]];
+                        kid_flags[c] = kids[c] < 0 ? nullptr : flags[(size_t)kids[c]];
+                    }
+                    LIBRECUDA_ERR_PROPAGATE(bind(streams[d]->ctx));
+                    LCU_LCB(lcb_bcast_tree_node(bufs[d], d == root ? nullptr : flags[(size_t)d], kid_bufs, kid_flags, body, chunk,
+                                                words / 2, epoch, 2000, ctas, streams[d]->main));
+                }
+                if (body < byteCount) {  // the last few bytes: plain stores from the root into every buffer
+                    LIBRECUDA_ERR_PROPAGATE(bind(streams[root]->ctx));
+                    const uint8_t *src = static_cast<const uint8_t *>(bufs[root]);
+                    for (int g = 0; g < nDev; ++g)
+                        if (g != root)
+                            LCU_LCB(lcb_copy_d2d(static_cast<uint8_t *>(bufs[g]) + body, src + body, byteCount - body, streams[root]->main));
+                }
+                LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));
+                g_last_broadcast_form = 5;
+                return rebind_current();
+            }
+            useNccl = nDev == 2 ? 0 : 2;
+        }
         if (useNccl == 4) {
             // Ring of kernels: one launch per GPU that receives and forwards in small chunks through flags in peer
             // memory.  All buffers must be 16-byte aligned; otherwise the engine chain runs.  Two kernels:

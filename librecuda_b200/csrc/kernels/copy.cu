@@ -709,6 +709,99 @@ __global__ void __launch_bounds__(512) ring_bcast_warp_kernel(const uint4 *__res
 }
 
 // ---------------------------------------------------------------------------------------------
+// tree broadcast: two complementary binary trees, one per half of the buffer
+// ---------------------------------------------------------------------------------------------
+// A chain of G GPUs pays G - 1 hops before the last one is done, each hop worth the chunks of all resident warps.
+// Here the first half of the chunks travels down one binary tree over the non-root GPUs and the second half down
+// another in which the inner nodes of the first are leaves: every GPU still receives each byte once and sends at
+// most one buffer's worth (an inner node stores its half to two children), but the depth is 1 + log2(G - 1).  One
+// kernel per GPU serves both halves: the warps are divided between the two roles, a role with children
+// forwards (the chunk-per-warp protocol of ring_bcast_warp_kernel, each vector stored once per child, one
+// release and one flag store per child), a role without children only waits for its chunks.
+struct TreeRole {
+    size_t c_lo, c_hi;             // this half: chunks [c_lo, c_hi) of the buffer
+    uint4 *child[2];               // the children's buffers (whole buffers, indexed like `local`); null = no child
+    unsigned int *child_flags[2];  // the children's flag arrays
+};
+struct TreeArgs {
+    TreeRole role[2];
+    unsigned int warps0;  // warps of the grid that work for role[0]; the others work for role[1]
+};
+
+template <bool ROOT>
+__global__ void __launch_bounds__(512) tree_bcast_kernel(const uint4 *__restrict__ local, const unsigned int *flags_in,
+                                                         const TreeArgs a, size_t nvec, size_t chunk_vec, unsigned int epoch,
+                                                         unsigned long long timeout_ns) {
+    const unsigned lane = threadIdx.x & 31u;
+    const size_t gw = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const size_t total = (size_t)gridDim.x * (blockDim.x >> 5);
+    const bool second = gw >= a.warps0;
+    const size_t w = second ? gw - a.warps0 : gw;
+    const size_t W = second ? total - a.warps0 : a.warps0;
+    const size_t c_lo = second ? a.role[1].c_lo : a.role[0].c_lo, c_hi = second ? a.role[1].c_hi : a.role[0].c_hi;
+    uint4 *const kid0 = second ? a.role[1].child[0] : a.role[0].child[0];
+    uint4 *const kid1 = second ? a.role[1].child[1] : a.role[0].child[1];
+    unsigned int *const kf0 = second ? a.role[1].child_flags[0] : a.role[0].child_flags[0];
+    unsigned int *const kf1 = second ? a.role[1].child_flags[1] : a.role[0].child_flags[1];
+    for (size_t c = c_lo + w; c < c_hi; c += W) {
+        if (!ROOT) {
+            bool ok = false;
+            unsigned long long t0, now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+            for (unsigned int polls = 0; polls < (1u << 26); ++polls) {  // uniform over the warp
+                unsigned int v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags_in + c) : "memory");
+                if ((int)(v - epoch) >= 0) {
+                    ok = true;
+                    break;
+                }
+                if (*(volatile unsigned int *)&g_ring_abort == epoch) break;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (now - t0 > timeout_ns) {
+                    if (lane == 0) {
+                        raise_error(kErrFlagTimeout);
+                        *(volatile unsigned int *)&g_ring_abort = epoch;
+                    }
+                    break;
+                }
+            }
+            if (!__all_sync(0xffffffffu, ok)) return;
+        }
+        if (kid0 != nullptr) {
+            const size_t first = c * chunk_vec;
+            const size_t end = first + chunk_vec < nvec ? first + chunk_vec : nvec;
+            constexpr int U = 8;
+            for (size_t base = first + lane; base < end; base += (size_t)U * 32) {
+                uint4 v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const size_t j = base + (size_t)u * 32;
+                    if (j < end) v[u] = ROOT ? ld_stream<2>(local + j) : ld_volatile_v4(local + j);
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const size_t j = base + (size_t)u * 32;
+                    if (j < end) st_stream<1>(kid0 + j, v[u]);
+                }
+                if (kid1 != nullptr) {
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const size_t j = base + (size_t)u * 32;
+                        if (j < end) st_stream<1>(kid1 + j, v[u]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {  // one release for both children, then the flags
+                asm volatile("fence.acq_rel.sys;" ::: "memory");
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" :: "l"(kf0 + c), "r"(epoch) : "memory");
+                if (kid1 != nullptr) asm volatile("st.relaxed.sys.global.u32 [%0], %1;" :: "l"(kf1 + c), "r"(epoch) : "memory");
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 namespace {
@@ -1011,6 +1104,8 @@ int preload_copy_kernels() {
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ring_bcast_kernel<false>);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ring_bcast_warp_kernel<true>);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ring_bcast_warp_kernel<false>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, tree_bcast_kernel<true>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, tree_bcast_kernel<false>);
     return (int)e;
 }
 }  // namespace lcb
@@ -1143,6 +1238,77 @@ extern "C" int lcb_bcast_ring_hop(const void *local, void *next, const void *fla
     }
     if (flags_in == nullptr) return launch_kernel(ring_bcast_kernel<true>, (unsigned)grid, 512, 0, st, l, n, fi, fn, nvec, chunk_vec, epoch, timeout_ns);
     return launch_kernel(ring_bcast_kernel<false>, (unsigned)grid, 512, 0, st, l, n, fi, fn, nvec, chunk_vec, epoch, timeout_ns);
+}
+
+extern "C" int lcb_bcast_tree_plan(int n_ranks, int root, int rank, int *parents, int *children) {
+    if (n_ranks < 2 || n_ranks > 64 || root < 0 || root >= n_ranks || rank < 0 || rank >= n_ranks) return 1;
+    if (parents == nullptr || children == nullptr) return 1;
+    const int m = n_ranks - 1;  // the non-root members: p(i) = root + 1 + i in heap order for the first tree,
+    auto p = [&](int i) { return (root + 1 + i) % n_ranks; };  // q(i) = p(m - 1 - i) for the second
+    for (int k = 0; k < 4; ++k) children[k] = -1;
+    if (rank == root) {
+        parents[0] = parents[1] = -1;
+        children[0] = p(0);
+        children[2] = p(m - 1);
+        return 0;
+    }
+    const int i = (rank - root - 1 + n_ranks) % n_ranks, j = m - 1 - i;
+    parents[0] = i == 0 ? root : p((i - 1) / 2);
+    if (2 * i + 1 < m) children[0] = p(2 * i + 1);
+    if (2 * i + 2 < m) children[1] = p(2 * i + 2);
+    parents[1] = j == 0 ? root : p(m - 1 - (j - 1) / 2);
+    if (2 * j + 1 < m) children[2] = p(m - 1 - (2 * j + 1));
+    if (2 * j + 2 < m) children[3] = p(m - 1 - (2 * j + 2));
+    return 0;
+}
+
+extern "C" int lcb_bcast_tree_node(const void *local, const void *flags_in, void *const *children, void *const *children_flags,
+                                   size_t bytes, size_t chunk_bytes, size_t split_chunk, unsigned int epoch,
+                                   unsigned int timeout_ms, int ctas, lcbStream stream) {
+    using namespace lcb;
+    if (bytes == 0) return 0;
+    if (local == nullptr || children == nullptr || children_flags == nullptr || epoch == 0 || ctas < 0) return 1;
+    if (timeout_ms == 0 || timeout_ms > 10000u) return 1;
+    if (chunk_bytes < 4096 || (chunk_bytes & 15) || (bytes & 15)) return 1;
+    if ((reinterpret_cast<uintptr_t>(local) & 15) || (reinterpret_cast<uintptr_t>(flags_in) & 3)) return 1;
+    const size_t nvec = bytes / 16, chunk_vec = chunk_bytes / 16;
+    const size_t nchunks = (nvec + chunk_vec - 1) / chunk_vec;
+    if (split_chunk > nchunks) return 1;
+    TreeArgs a{};
+    bool forwards[2] = {false, false};
+    for (int r = 0; r < 2; ++r) {
+        a.role[r].c_lo = r == 0 ? 0 : split_chunk;
+        a.role[r].c_hi = r == 0 ? split_chunk : nchunks;
+        int filled = 0;
+        for (int k = 0; k < 2; ++k) {  // children are packed to the front: the kernel tests child[0] first
+            void *c = children[2 * r + k], *f = children_flags[2 * r + k];
+            if (c == nullptr) continue;
+            if (f == nullptr || (reinterpret_cast<uintptr_t>(c) & 15) || (reinterpret_cast<uintptr_t>(f) & 3)) return 1;
+            a.role[r].child[filled] = static_cast<uint4 *>(c);
+            a.role[r].child_flags[filled] = static_cast<unsigned int *>(f);
+            ++filled;
+        }
+        forwards[r] = filled > 0;
+    }
+    if (flags_in == nullptr && !forwards[0] && !forwards[1]) return 0;  // a root without children
+    size_t grid = ctas > 0 ? (size_t)ctas : (size_t)sm_count();
+    if (grid * 16 > nchunks + 16) grid = (nchunks + 16) / 16;
+    if (grid < 2) grid = 2;  // at least a CTA's worth of warps per role
+    const size_t total = grid * 16;
+    // a role that only waits needs few warps (a poll costs about a microsecond, a chunk arrives every 50 ns)
+    size_t waiters = total / 4 < 128 ? total / 4 : 128;
+    if (waiters < 16) waiters = 16;
+    size_t warps0 = total / 2;
+    if (forwards[0] && !forwards[1]) warps0 = total - waiters;
+    if (!forwards[0] && forwards[1]) warps0 = waiters;
+    a.warps0 = (unsigned int)warps0;
+    NoPdlScope plain(true);  // a kernel that polls must not sit on the SMs before its predecessor on the stream is done
+    const unsigned long long timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint4 *l = static_cast<const uint4 *>(local);
+    const unsigned int *fi = static_cast<const unsigned int *>(flags_in);
+    if (flags_in == nullptr) return launch_kernel(tree_bcast_kernel<true>, (unsigned)grid, 512, 0, st, l, fi, a, nvec, chunk_vec, epoch, timeout_ns);
+    return launch_kernel(tree_bcast_kernel<false>, (unsigned)grid, 512, 0, st, l, fi, a, nvec, chunk_vec, epoch, timeout_ns);
 }
 
 extern "C" int lcb_flag_post(void *flag, unsigned int value, lcbStream stream) {

@@ -310,7 +310,7 @@ def test_lockstep_engine_all_to_all_recorded(gpus):
     ctxs[0].set_current()
 
 
-@pytest.mark.parametrize("use_nccl", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("use_nccl", [0, 1, 2, 3, 4, 5])
 @pytest.mark.parametrize("root", [0, 1])
 def test_broadcast(gpus, use_nccl, root):
     ctxs, streams = gpus
@@ -318,7 +318,7 @@ def test_broadcast(gpus, use_nccl, root):
     n = 37 * MiB + 1001
     api.tune(bcast_engine_piece_mib=4)     # form 2 with more than two GPUs: ten pieces, the last one ragged
     api.tune(bcast_mc_piece_mib=4, bcast_mc_slots=3)   # form 3: ten pieces through a ring of three slots, ragged end
-    api.tune(bcast_ring_chunk_kib=16, bcast_ring_ctas=37)   # form 4: 2369 chunks over 37 CTAs, the last chunk ragged
+    api.tune(bcast_ring_chunk_kib=16, bcast_ring_ctas=37)   # forms 4 and 5: 2369 chunks over 37 CTAs, the last chunk ragged
     try:
         _broadcast(ctxs, streams, G, n, use_nccl, root)
     finally:
@@ -336,6 +336,27 @@ def test_ring_broadcast_chunk_per_warp_and_per_cta(gpus, per_warp, chunk_kib, ct
     try:
         _broadcast(ctxs, streams, G, 37 * MiB + 1001, 4, G - 1)
         _broadcast(ctxs, streams, G, 37 * MiB + 1001, 4, G - 1)
+    finally:
+        api.tune_reset()
+    for g in range(G):
+        ctxs[g].set_current()
+        assert api.device_error_word() == 0
+    ctxs[0].set_current()
+
+
+@pytest.mark.parametrize("chunk_kib,ctas", [(4, 2), (8, 5), (0, 0)])
+def test_two_tree_broadcast(gpus, chunk_kib, ctas):
+    # Form 5: few warps and small chunks (every warp of either role takes many turns; an odd number of chunks, the
+    # last one ragged) and the shapes the library picks; every rank as root in turn, so that every rank is inner
+    # node, leaf and root of both trees; then a buffer of less than one chunk and one of two chunks.
+    ctxs, streams = gpus
+    G = len(ctxs)
+    api.tune(bcast_ring_chunk_kib=chunk_kib, bcast_ring_ctas=ctas)
+    try:
+        for root in range(G):
+            _broadcast(ctxs, streams, G, 21 * MiB + 1001, 5, root)
+        _broadcast(ctxs, streams, G, 1040, 5, 0)
+        _broadcast(ctxs, streams, G, 2 * (chunk_kib or 16) * 1024, 5, G - 1)
     finally:
         api.tune_reset()
     for g in range(G):
