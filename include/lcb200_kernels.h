@@ -132,7 +132,9 @@ int lcb_flag_wait(const void *flag, unsigned int value, unsigned int timeout_ms,
  * them, zero before the first use, epochs grow from call to call.  `bytes` and both buffers are multiples of
  * 16; a wait is bounded by timeout_ms (1..10000: then bit 1 of the sticky error word, and the kernel returns).
  * ctas = 0: two CTAs per SM.  A chunk is the work of one warp (tunable "bcast_ring_warp" = 1, the default;
- * chunks of 8-32 KiB) or of one CTA (= 0; chunks from 128 KiB); every GPU of a chain must run the same form.
+ * chunks of 8-32 KiB, handed to the warps by ticket unless "bcast_ring_tickets" = 0) or of one CTA (= 0; chunks
+ * from 128 KiB); every GPU of a chain must run the same form.  One broadcast at a time per GPU: the ticket
+ * counters and the abort word are per GPU.
  * ref: none (single-GPU reference, librecuda.cpp:61). */
 int lcb_bcast_ring_hop(const void *local, void *next, const void *flags_in, void *flags_next, size_t bytes, size_t chunk_bytes,
                        unsigned int epoch, unsigned int timeout_ms, int ctas, lcbStream stream);

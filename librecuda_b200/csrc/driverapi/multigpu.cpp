@@ -534,12 +534,15 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
         for (int r = 0; r < nDev; ++r) mains[(size_t)r] = streams[r]->main;
         if (useNccl == 5) {
             // Two complementary binary trees of fused kernels (tree_bcast_kernel, lcb_bcast_tree_plan): half of the
-            // chunks per tree, one launch per GPU.  Same requirements and fall-back as the ring.
+            // chunks per tree, one launch per GPU, 8 KiB chunks by ticket, one CTA per SM.  Same requirements and
+            // fall-back as the ring.  Measured, 4 GiB / 1 GiB: 683 / 637 GB/s at 8 GPUs (ring 678 / 612, NCCL 668 /
+            // 633), 694 / 669 at 4 (ring 693 / 663, NCCL 673 / 649); time = bytes / 690 GB/s + 0.18 ms at 8 GPUs.  More
+            // than one CTA per SM is slower here (577-589 with 222 / 296 CTAs).
             bool aligned = true;
             for (int r = 0; r < nDev; ++r) aligned = aligned && (reinterpret_cast<uintptr_t>(bufs[r]) & 15) == 0;
             const size_t body = byteCount & ~(size_t)15;
             if (aligned && body > 0) {
-                const int chunk_kib = lcb_tune_get("bcast_ring_chunk_kib") > 0 ? lcb_tune_get("bcast_ring_chunk_kib") : 16;
+                const int chunk_kib = lcb_tune_get("bcast_ring_chunk_kib") > 0 ? lcb_tune_get("bcast_ring_chunk_kib") : 8;
                 const size_t chunk = (size_t)chunk_kib << 10;
                 const size_t words = (body + chunk - 1) / chunk;
                 std::vector<unsigned int *> flags((size_t)nDev, nullptr);
@@ -576,10 +579,11 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
         if (useNccl == 4) {
             // Ring of kernels: one launch per GPU that receives and forwards in small chunks through flags in peer
             // memory.  All buffers must be 16-byte aligned; otherwise the engine chain runs.  Two kernels:
-            //   one chunk per warp (ring_bcast_warp_kernel, the default): 16 KiB chunks; 148 CTAs up to 4 GPUs, 111
-            //     beyond.  Measured, 4 GiB: 687 GB/s at 4 GPUs (NCCL 670, engine chain 689), 669-674 at 8 (NCCL 665).
-            //     Time = bytes / 705 GB/s + 0.15 ms at 4 GPUs, + 0.30 ms at 8: every hop adds about the time the chunks
-            //     of all resident warps take to drain (28-37 MiB), which is why fewer CTAs win on the longer chain.
+            //   one chunk per warp (ring_bcast_warp_kernel, the default): 8 KiB chunks handed out by ticket, one CTA
+            //     per SM.  Measured, 4 GiB: 693 GB/s at 4 GPUs (NCCL 673, engine chain 689), 676-678 at 8 (NCCL 668);
+            //     with a fixed stride instead of tickets 671-687 / 641-673 and a strong dependence on the grid.
+            //     Time = bytes / 705 GB/s + 0.15 ms at 4 GPUs, + 0.25-0.30 ms at 8: every hop adds about the time
+            //     the chunks in flight take to drain, which is what the two trees of form 5 shorten.
             //   one chunk per CTA (ring_bcast_kernel, tunable bcast_ring_warp = 0): 128 KiB chunks x 296 CTAs, 676 at 4
             //     GPUs and 654 at 8 (+ 0.22 / 0.47 ms); 590 with 64 KiB, 369 with 32 KiB chunks, because the whole CTA
             //     idles while one thread's release waits for the remote stores to be acknowledged.
@@ -588,7 +592,7 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
             const size_t body = byteCount & ~(size_t)15;
             if (aligned && body > 0) {
                 const bool per_warp = lcb_tune_get("bcast_ring_warp") != 0;
-                const int chunk_kib = lcb_tune_get("bcast_ring_chunk_kib") > 0 ? lcb_tune_get("bcast_ring_chunk_kib") : (per_warp ? 16 : 128);
+                const int chunk_kib = lcb_tune_get("bcast_ring_chunk_kib") > 0 ? lcb_tune_get("bcast_ring_chunk_kib") : (per_warp ? 8 : 128);
                 const size_t chunk = (size_t)chunk_kib << 10;
                 const size_t words = (body + chunk - 1) / chunk;
                 std::vector<unsigned int *> flags((size_t)nDev, nullptr);
@@ -596,11 +600,8 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
                 LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));  // nobody may still be reading or writing the buffers
                 const unsigned int epoch = ++g_ring_epoch;
                 int ctas = lcb_tune_get("bcast_ring_ctas");
-                if (ctas <= 0 && per_warp) {  // per SM: one CTA up to 4 GPUs, three quarters of one beyond
-                    int sms = 0;
-                    LCU_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, devs[(size_t)root]));
-                    ctas = nDev <= 4 ? sms : (sms * 3) / 4;
-                }
+                if (ctas <= 0 && per_warp)  // one CTA per SM (the per-CTA form takes its own default, two per SM)
+                    LCU_CUDA(cudaDeviceGetAttribute(&ctas, cudaDevAttrMultiProcessorCount, devs[(size_t)root]));
                 for (int k = 0; k < nDev; ++k) {
                     const int d = (root + k) % nDev, nx = (root + k + 1) % nDev;
                     const bool last = k + 1 == nDev;

@@ -51,12 +51,13 @@ struct Tuning {
     int phase_chunk;             // phase-grouped copy: bytes per bulk copy
     int phase_stages;            // phase-grouped copy: bulk copies per CTA and phase (2, 3, 4, 6, 12 or 24)
     int phase_ns;                // phase-grouped copy: length of a load / store time slice in ns (0: no slicing)
-    int bcast_ring_chunk_kib;    // ring-of-kernels broadcast: KiB per chunk (one flag word each); 0: 16 per warp, 128 per CTA
-    int bcast_ring_ctas;         // ring-of-kernels broadcast: CTAs per GPU (0: chosen from the form and the number of GPUs)
+    int bcast_ring_chunk_kib;    // ring-of-kernels broadcast: KiB per chunk (one flag word each); 0: 8 per warp, 128 per CTA
+    int bcast_ring_ctas;         // ring-of-kernels broadcast: CTAs per GPU (0: one per SM with a chunk per warp, two with a chunk per CTA)
     int bcast_mc_piece_mib;      // multicast broadcast: MiB per piece
     int bcast_mc_slots;          // multicast broadcast: pieces in the staging ring of every GPU
     int bcast_mc_ctas;           // multicast broadcast: looping CTAs of the root's store kernel (0: one short CTA per tile)
     int bcast_ring_warp;         // ring-of-kernels broadcast: 1 = one chunk (and flag) per warp, 0 = per CTA
+    int bcast_ring_tickets;      // ring / tree broadcast, chunk per warp: 1 = chunks handed out by ticket, 0 = by a fixed stride
 };
 Tuning &tuning();
 

@@ -648,20 +648,46 @@ __global__ void __launch_bounds__(512) ring_bcast_kernel(const uint4 *__restrict
     }
 }
 
-// The same protocol with one chunk per WARP (a few KiB, one flag word each): a warp polls, loads, stores, posts and
-// moves on by itself, so nothing in the CTA idles while one warp's release waits for its remote stores to be
+// Chunks handed out by ticket instead of by a fixed stride: a warp that is done takes the oldest chunk nobody has
+// taken yet, so a slow warp (an SM that carries more CTAs, a late flag) delays one chunk and not every W-th.  The
+// ticket counters are per GPU; the last warp to leave a kernel sets them back to zero for the next launch (the
+// kernels that use them are launched without programmatic overlap and one broadcast at a time per GPU).
+__device__ unsigned int g_bcast_ticket[2] = {0, 0};
+__device__ unsigned int g_bcast_exit = 0;
+
+__device__ __forceinline__ unsigned int take_ticket(int role, unsigned lane) {
+    unsigned int t = 0;
+    if (lane == 0) t = atomicAdd(&g_bcast_ticket[role], 1u);
+    return __shfl_sync(0xffffffffu, t, 0);
+}
+__device__ __forceinline__ void leave_tickets(unsigned lane, unsigned int total_warps) {
+    __syncwarp();
+    if (lane == 0) {
+        __threadfence();
+        if (atomicAdd(&g_bcast_exit, 1u) == total_warps - 1) {
+            g_bcast_ticket[0] = 0;
+            g_bcast_ticket[1] = 0;
+            __threadfence();
+            g_bcast_exit = 0;
+        }
+    }
+}
+
+// The same protocol with one chunk per WARP (8 KiB by default, one flag word each): a warp polls, loads, stores, posts
+// and moves on by itself, so nothing in the CTA idles while one warp's release waits for its remote stores to be
 // acknowledged, and a byte can be forwarded a few microseconds after it arrived instead of after the time all
 // CTAs' chunks take to drain.  Every lane polls the flag (one request per warp: same address) and so holds its
 // own acquire; the release is lane 0's, after a warp barrier, and is cumulative over what the barrier ordered
-// before it.  Warp w of the grid handles chunks w, w + W, ...
-template <bool ROOT>
+// before it.  Chunks go to the warps by ticket (DYN) or by a fixed stride: warp w handles chunks w, w + W, ...
+template <bool ROOT, bool DYN>
 __global__ void __launch_bounds__(512) ring_bcast_warp_kernel(const uint4 *__restrict__ local, uint4 *__restrict__ next,
                                                               const unsigned int *flags_in, unsigned int *flags_next, size_t nvec,
                                                               size_t chunk_vec, unsigned int epoch, unsigned long long timeout_ns) {
     const unsigned lane = threadIdx.x & 31u;
     const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
     const size_t nchunks = (nvec + chunk_vec - 1) / chunk_vec;
-    for (size_t c = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); c < nchunks; c += warps) {
+    for (size_t c = DYN ? take_ticket(0, lane) : (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); c < nchunks;
+         c = DYN ? take_ticket(0, lane) : c + warps) {
         if (!ROOT) {
             bool ok = false;
             unsigned long long t0, now;
@@ -683,7 +709,7 @@ __global__ void __launch_bounds__(512) ring_bcast_warp_kernel(const uint4 *__res
                     break;
                 }
             }
-            if (!__all_sync(0xffffffffu, ok)) return;
+            if (!__all_sync(0xffffffffu, ok)) break;
         }
         if (next != nullptr) {
             const size_t first = c * chunk_vec;
@@ -706,6 +732,7 @@ __global__ void __launch_bounds__(512) ring_bcast_warp_kernel(const uint4 *__res
             if (lane == 0) asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(flags_next + c), "r"(epoch) : "memory");
         }
     }
+    if (DYN) leave_tickets(lane, (unsigned int)warps);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -728,7 +755,7 @@ struct TreeArgs {
     unsigned int warps0;  // warps of the grid that work for role[0]; the others work for role[1]
 };
 
-template <bool ROOT>
+template <bool ROOT, bool DYN>
 __global__ void __launch_bounds__(512) tree_bcast_kernel(const uint4 *__restrict__ local, const unsigned int *flags_in,
                                                          const TreeArgs a, size_t nvec, size_t chunk_vec, unsigned int epoch,
                                                          unsigned long long timeout_ns) {
@@ -743,7 +770,8 @@ __global__ void __launch_bounds__(512) tree_bcast_kernel(const uint4 *__restrict
     uint4 *const kid1 = second ? a.role[1].child[1] : a.role[0].child[1];
     unsigned int *const kf0 = second ? a.role[1].child_flags[0] : a.role[0].child_flags[0];
     unsigned int *const kf1 = second ? a.role[1].child_flags[1] : a.role[0].child_flags[1];
-    for (size_t c = c_lo + w; c < c_hi; c += W) {
+    for (size_t c = c_lo + (DYN ? take_ticket(second ? 1 : 0, lane) : w); c < c_hi;
+         c = DYN ? c_lo + take_ticket(second ? 1 : 0, lane) : c + W) {
         if (!ROOT) {
             bool ok = false;
             unsigned long long t0, now;
@@ -765,7 +793,7 @@ __global__ void __launch_bounds__(512) tree_bcast_kernel(const uint4 *__restrict
                     break;
                 }
             }
-            if (!__all_sync(0xffffffffu, ok)) return;
+            if (!__all_sync(0xffffffffu, ok)) break;
         }
         if (kid0 != nullptr) {
             const size_t first = c * chunk_vec;
@@ -799,6 +827,7 @@ __global__ void __launch_bounds__(512) tree_bcast_kernel(const uint4 *__restrict
             }
         }
     }
+    if (DYN) leave_tickets(lane, (unsigned int)total);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1102,10 +1131,14 @@ int preload_copy_kernels() {
     // kernels that wait for another GPU's kernel must not meet a module load at their first launch
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ring_bcast_kernel<true>);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ring_bcast_kernel<false>);
-    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ring_bcast_warp_kernel<true>);
-    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ring_bcast_warp_kernel<false>);
-    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, tree_bcast_kernel<true>);
-    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, tree_bcast_kernel<false>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ring_bcast_warp_kernel<true, false>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ring_bcast_warp_kernel<false, false>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ring_bcast_warp_kernel<true, true>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ring_bcast_warp_kernel<false, true>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, tree_bcast_kernel<true, false>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, tree_bcast_kernel<false, false>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, tree_bcast_kernel<true, true>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, tree_bcast_kernel<false, true>);
     return (int)e;
 }
 }  // namespace lcb
@@ -1233,8 +1266,10 @@ extern "C" int lcb_bcast_ring_hop(const void *local, void *next, const void *fla
     unsigned int *fn = static_cast<unsigned int *>(flags_next);
     if (tuning().bcast_ring_warp) {  // one chunk per warp: 16 warps per CTA share the chunks
         if (grid * 16 > nchunks) grid = (nchunks + 15) / 16;
-        if (flags_in == nullptr) return launch_kernel(ring_bcast_warp_kernel<true>, (unsigned)grid, 512, 0, st, l, n, fi, fn, nvec, chunk_vec, epoch, timeout_ns);
-        return launch_kernel(ring_bcast_warp_kernel<false>, (unsigned)grid, 512, 0, st, l, n, fi, fn, nvec, chunk_vec, epoch, timeout_ns);
+        const bool dyn = tuning().bcast_ring_tickets != 0;
+        auto kernel = flags_in == nullptr ? (dyn ? ring_bcast_warp_kernel<true, true> : ring_bcast_warp_kernel<true, false>)
+                                          : (dyn ? ring_bcast_warp_kernel<false, true> : ring_bcast_warp_kernel<false, false>);
+        return launch_kernel(kernel, (unsigned)grid, 512, 0, st, l, n, fi, fn, nvec, chunk_vec, epoch, timeout_ns);
     }
     if (flags_in == nullptr) return launch_kernel(ring_bcast_kernel<true>, (unsigned)grid, 512, 0, st, l, n, fi, fn, nvec, chunk_vec, epoch, timeout_ns);
     return launch_kernel(ring_bcast_kernel<false>, (unsigned)grid, 512, 0, st, l, n, fi, fn, nvec, chunk_vec, epoch, timeout_ns);
@@ -1307,8 +1342,10 @@ extern "C" int lcb_bcast_tree_node(const void *local, const void *flags_in, void
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint4 *l = static_cast<const uint4 *>(local);
     const unsigned int *fi = static_cast<const unsigned int *>(flags_in);
-    if (flags_in == nullptr) return launch_kernel(tree_bcast_kernel<true>, (unsigned)grid, 512, 0, st, l, fi, a, nvec, chunk_vec, epoch, timeout_ns);
-    return launch_kernel(tree_bcast_kernel<false>, (unsigned)grid, 512, 0, st, l, fi, a, nvec, chunk_vec, epoch, timeout_ns);
+    const bool dyn = tuning().bcast_ring_tickets != 0;
+    auto kernel = flags_in == nullptr ? (dyn ? tree_bcast_kernel<true, true> : tree_bcast_kernel<true, false>)
+                                      : (dyn ? tree_bcast_kernel<false, true> : tree_bcast_kernel<false, false>);
+    return launch_kernel(kernel, (unsigned)grid, 512, 0, st, l, fi, a, nvec, chunk_vec, epoch, timeout_ns);
 }
 
 extern "C" int lcb_flag_post(void *flag, unsigned int value, lcbStream stream) {

@@ -54,6 +54,7 @@ static const Tuning kDefaults = {
         /*bcast_mc_slots*/ 2,
         /*bcast_mc_ctas*/ 64,
         /*bcast_ring_warp*/ 1,
+        /*bcast_ring_tickets*/ 1,
 };
 
 static void apply_env_overrides() {  // LCB_TUNE="knob=value,knob=value": overrides for experiments
@@ -104,7 +105,7 @@ static bool knob_value_ok(const char *name, int v) {
     if (is("memset_path")) return v >= 0 && v <= 2;
     if (is("memset_issuers")) return v >= 1 && v <= 8;
     if (is("memset_bulk_ctas_sm")) return v >= 1 && v <= 32;
-    if (is("tma_cache_hint") || is("memset_cache_hint") || is("pdl") || is("bcast_ring_warp")) return v == 0 || v == 1;
+    if (is("tma_cache_hint") || is("memset_cache_hint") || is("pdl") || is("bcast_ring_warp") || is("bcast_ring_tickets")) return v == 0 || v == 1;
     if (is("auto_tma_min_mib")) return v >= -1;
     if (is("copy_vec_smem_pad") || is("tma_smem_pad") || is("memset_smem_pad")) return v >= 0 && v <= 200 * 1024;
     if (is("bcast_pull_ctas")) return v >= 0 && v <= 65536;
@@ -172,7 +173,8 @@ int check_launch() { return (int)cudaGetLastError(); }
     X(bcast_mc_piece_mib) \
     X(bcast_mc_slots) \
     X(bcast_mc_ctas) \
-    X(bcast_ring_warp)
+    X(bcast_ring_warp) \
+    X(bcast_ring_tickets)
 
 extern "C" int lcb_tune(const char *name, int value) {
     using lcb::tuning;

@@ -325,14 +325,15 @@ def test_broadcast(gpus, use_nccl, root):
         api.tune_reset()
 
 
-@pytest.mark.parametrize("per_warp,chunk_kib,ctas", [(1, 8, 5), (1, 0, 0), (0, 16, 37), (0, 0, 0)])
-def test_ring_broadcast_chunk_per_warp_and_per_cta(gpus, per_warp, chunk_kib, ctas):
-    # Form 4 with either kernel: a chunk (and its flag) per warp or per CTA, with few workers and small chunks
-    # (every worker takes many turns, the last chunk ragged) and with the shapes the library picks; the last GPU
-    # of the chain as root, twice in a row (the second call waits on the next epoch of the same flag words).
+@pytest.mark.parametrize("per_warp,chunk_kib,ctas,tickets", [(1, 8, 5, 1), (1, 8, 5, 0), (1, 0, 0, 1), (0, 16, 37, 0), (0, 0, 0, 0)])
+def test_ring_broadcast_chunk_per_warp_and_per_cta(gpus, per_warp, chunk_kib, ctas, tickets):
+    # Form 4 with either kernel: a chunk (and its flag) per warp -- handed out by ticket or by a fixed stride -- or
+    # per CTA, with few workers and small chunks (every worker takes many turns, the last chunk ragged) and with
+    # the shapes the library picks; the last GPU of the chain as root, twice in a row (the second call waits on
+    # the next epoch of the same flag words and starts from ticket counters the first call must have reset).
     ctxs, streams = gpus
     G = len(ctxs)
-    api.tune(bcast_ring_warp=per_warp, bcast_ring_chunk_kib=chunk_kib, bcast_ring_ctas=ctas)
+    api.tune(bcast_ring_warp=per_warp, bcast_ring_chunk_kib=chunk_kib, bcast_ring_ctas=ctas, bcast_ring_tickets=tickets)
     try:
         _broadcast(ctxs, streams, G, 37 * MiB + 1001, 4, G - 1)
         _broadcast(ctxs, streams, G, 37 * MiB + 1001, 4, G - 1)
@@ -344,19 +345,19 @@ def test_ring_broadcast_chunk_per_warp_and_per_cta(gpus, per_warp, chunk_kib, ct
     ctxs[0].set_current()
 
 
-@pytest.mark.parametrize("chunk_kib,ctas", [(4, 2), (8, 5), (0, 0)])
-def test_two_tree_broadcast(gpus, chunk_kib, ctas):
+@pytest.mark.parametrize("chunk_kib,ctas,tickets", [(4, 2, 1), (4, 2, 0), (8, 5, 1), (0, 0, 1)])
+def test_two_tree_broadcast(gpus, chunk_kib, ctas, tickets):
     # Form 5: few warps and small chunks (every warp of either role takes many turns; an odd number of chunks, the
     # last one ragged) and the shapes the library picks; every rank as root in turn, so that every rank is inner
     # node, leaf and root of both trees; then a buffer of less than one chunk and one of two chunks.
     ctxs, streams = gpus
     G = len(ctxs)
-    api.tune(bcast_ring_chunk_kib=chunk_kib, bcast_ring_ctas=ctas)
+    api.tune(bcast_ring_chunk_kib=chunk_kib, bcast_ring_ctas=ctas, bcast_ring_tickets=tickets)
     try:
         for root in range(G):
             _broadcast(ctxs, streams, G, 21 * MiB + 1001, 5, root)
         _broadcast(ctxs, streams, G, 1040, 5, 0)
-        _broadcast(ctxs, streams, G, 2 * (chunk_kib or 16) * 1024, 5, G - 1)
+        _broadcast(ctxs, streams, G, 2 * (chunk_kib or 8) * 1024, 5, G - 1)
     finally:
         api.tune_reset()
     for g in range(G):
