@@ -52,3 +52,20 @@ def test_plan_refuses_bad_arguments():
     assert N.lib.lcb_bcast_tree_plan(4, 4, 0, parents, kids) != 0
     assert N.lib.lcb_bcast_tree_plan(4, 0, -1, parents, kids) != 0
     assert N.lib.lcb_bcast_tree_plan(4, 0, 1, None, kids) != 0
+
+
+def test_node_launcher_refuses_bad_arguments_before_touching_the_gpu():
+    four = (C.c_void_p * 4)()
+    buf = C.c_void_p(0x10000)
+    call = N.lib.lcb_bcast_tree_node
+    assert call(buf, None, four, four, 0, 8192, 0, 1, 100, 0, None) == 0              # nothing to do
+    assert call(None, None, four, four, 1 << 20, 8192, 64, 1, 100, 0, None) != 0       # no buffer
+    assert call(buf, None, four, four, 1 << 20, 8192, 64, 0, 100, 0, None) != 0        # epoch 0 is "never posted"
+    assert call(buf, None, four, four, 1 << 20, 2048, 64, 1, 100, 0, None) != 0        # chunk too small
+    assert call(buf, None, four, four, (1 << 20) + 8, 8192, 64, 1, 100, 0, None) != 0  # not whole vectors
+    assert call(C.c_void_p(0x10008), None, four, four, 1 << 20, 8192, 64, 1, 100, 0, None) != 0  # misaligned
+    assert call(buf, None, four, four, 1 << 20, 8192, 64, 1, 0, 0, None) != 0          # unbounded wait
+    assert call(buf, None, four, four, 1 << 20, 8192, 129, 1, 100, 0, None) != 0       # split beyond the last chunk
+    kids = (C.c_void_p * 4)(0x20000, None, None, None)
+    assert call(buf, None, kids, four, 1 << 20, 8192, 64, 1, 100, 0, None) != 0        # a child without flags
+    assert call(buf, None, four, four, 1 << 20, 8192, 64, 1, 100, 0, None) == 0        # a root without children
