@@ -131,7 +131,7 @@ int lcb_flag_wait(const void *flag, unsigned int value, unsigned int timeout_ms,
  * at the same time; flags_* are arrays of one unsigned int per chunk in the memory of the GPU that waits on
  * them, zero before the first use, epochs grow from call to call.  `bytes` and both buffers are multiples of
  * 16; a wait is bounded by timeout_ms (1..10000: then bit 1 of the sticky error word, and the kernel returns).
- * ctas = 0: two CTAs per SM.  A chunk is the work of one warp (tunable "bcast_ring_warp" = 1, the default;
+ * ctas = 0: one CTA per SM (two in the chunk-per-CTA form).  A chunk is the work of one warp (tunable "bcast_ring_warp" = 1, the default;
  * chunks of 8-32 KiB, handed to the warps by ticket unless "bcast_ring_tickets" = 0) or of one CTA (= 0; chunks
  * from 128 KiB); every GPU of a chain must run the same form.  One broadcast at a time per GPU: the ticket
  * counters and the abort word are per GPU.

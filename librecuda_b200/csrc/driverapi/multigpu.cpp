@@ -599,9 +599,7 @@ libreCudaStatus_t libreCuBroadcast(void *const *bufs, int root, size_t byteCount
                 for (int r = 0; r < nDev; ++r) LIBRECUDA_ERR_PROPAGATE(ring_flags_for(devs[(size_t)r], words, &flags[(size_t)r]));
                 LIBRECUDA_ERR_PROPAGATE(cross_join(nDev, streams));  // nobody may still be reading or writing the buffers
                 const unsigned int epoch = ++g_ring_epoch;
-                int ctas = lcb_tune_get("bcast_ring_ctas");
-                if (ctas <= 0 && per_warp)  // one CTA per SM (the per-CTA form takes its own default, two per SM)
-                    LCU_CUDA(cudaDeviceGetAttribute(&ctas, cudaDevAttrMultiProcessorCount, devs[(size_t)root]));
+                const int ctas = lcb_tune_get("bcast_ring_ctas");  // 0: one CTA per SM with a chunk per warp, two per CTA
                 for (int k = 0; k < nDev; ++k) {
                     const int d = (root + k) % nDev, nx = (root + k + 1) % nDev;
                     const bool last = k + 1 == nDev;

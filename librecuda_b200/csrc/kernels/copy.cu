@@ -1255,7 +1255,7 @@ extern "C" int lcb_bcast_ring_hop(const void *local, void *next, const void *fla
     if (next == nullptr && flags_in == nullptr) return 0;  // neither receives nor forwards: nothing to do
     const size_t nvec = bytes / 16, chunk_vec = chunk_bytes / 16;
     const size_t nchunks = (nvec + chunk_vec - 1) / chunk_vec;
-    size_t grid = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * 2;
+    size_t grid = ctas > 0 ? (size_t)ctas : (size_t)sm_count() * (tuning().bcast_ring_warp ? 1 : 2);
     if (grid > nchunks) grid = nchunks;
     NoPdlScope plain(true);  // a kernel that polls must not sit on the SMs before its predecessor on the stream is done
     const unsigned long long timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
