@@ -99,5 +99,6 @@ def test_the_replay_notices_a_broken_topology():
     children[2] = ([], [])
     rng = random.Random(5)
     arrived, left, parked = simulate(n, root, children, 20, 20, [[3, 1]] * n, rng)
-    assert parked and all(g == 3 for g, _ in parked)
-    assert arrived[4] == [0] * 20 and left[3] < 4
+    assert {g for g, _ in parked} == {3, 4}
+    assert arrived[3] == [0] * 20 and arrived[4] == [0] * 20 and left[3] < 4 and left[4] < 4
+    assert arrived[1] == [1] * 20 and arrived[2] == [1] * 20 and left[0] == 4
